@@ -143,6 +143,17 @@ class CallView:
     def __len__(self) -> int:
         return len(self.parts) if self.parts else (0 if self.storage is None else 1)
 
+    def sub(self, lo: int, hi: int) -> "CallView":
+        """The view of needs lo .. hi - 1 of this call's declaration: what a part hands to a part inside it (a layer
+        to its mixer, a mixer of several branches to each branch)."""
+        parts = (self.parts if self.parts else ((self,) if self.storage is not None else ()))[lo:hi]
+        if not parts:
+            return CallView(self.call, -1, None, None, True)
+        if len(parts) == 1:
+            return parts[0]
+        first = parts[0]
+        return CallView(self.call, first.group, first.storage, first.need, first.owner, tuple(parts))
+
 
 def _as_needs(need) -> Tuple[object, ...]:
     """A call's declaration as a tuple of needs: none, one, or several."""

@@ -209,7 +209,13 @@ class RoutedExpertsSpec:
     logits (float32), weighted by the softmax over those logits alone (which equals the softmax over all logits
     divided by the chosen ones' sum) times `route_scale`. `limit` 0: the experts are SwiGLU units; > 0: clamped gated
     units with that limit, `alpha` and `up_shift` (ClampedGLUSpec). `shared`: a clamped gated unit that every token
-    uses, added to the sum times sigmoid(x . w) of the one-row matrix names["shared_gate"]."""
+    uses, added to the sum times sigmoid(x . w) of the one-row matrix names["shared_gate"].
+
+    `score` "sigmoid": a token's scores are the sigmoids of its router logits instead; the experts are chosen by score plus
+    a learned number per expert (`correction`, names["correction"]; the weights are the scores without it), among the
+    `keep_groups` of `groups` equal groups of neighbouring experts whose `group_top` largest such sums add up highest
+    (experts of the other groups cannot be chosen); the weights are the chosen scores times `route_scale`, divided by their
+    sum only with `renorm`. `activation` "relu_squared": an expert is down(max(up x, 0)^2), without a gate matrix."""
     hidden: int
     intermediate: int
     experts: int
@@ -221,8 +227,61 @@ class RoutedExpertsSpec:
     shared: Optional["ClampedGLUSpec"] = None
     names: Dict[str, str] = field(default_factory=lambda: {
         "router": "mlp.router", "gate": "mlp.e{e}.gate", "up": "mlp.e{e}.up", "down": "mlp.e{e}.down",
-        "shared_gate": "mlp.shared.sg"})
+        "shared_gate": "mlp.shared.sg", "correction": "mlp.correction"})
     kind: str = "routed_experts"
+    score: str = "softmax"           # "softmax" over the chosen logits | "sigmoid" of each logit
+    correction: bool = False         # sigmoid scores: a learned number per expert joins the score for the choice only
+    groups: int = 1
+    keep_groups: int = 1
+    group_top: int = 2
+    renorm: bool = False
+    activation: str = "gated"        # "gated" (SwiGLU, or the clamped unit with `limit`) | "relu_squared"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """A gated delta-rule memory per head: a state [dim, vdim] (float32) that each token decays by
+    exp(-exp(A_log) softplus(a x + dt_bias)), corrects by beta = sigmoid(b x) towards its value along its unit-length key,
+    and reads with its unit-length query times dim^(-1/2) (parts/gated_delta.py has the formulas). q and k (`kv_heads`
+    heads of `dim`, shared by heads / kv_heads heads each) and v (`heads` of `vdim`) each pass a causal per-channel filter
+    of `taps` taps and silu. The heads' outputs are divided by their root mean square (`eps`), multiplied by a weight of
+    `vdim` entries that the heads share and by silu of an output gate, then projected."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    taps: int
+    eps: float
+    unit_eps: float = 1e-6
+    names: Dict[str, str] = field(default_factory=lambda: {
+        "q": "mix.q", "k": "mix.k", "v": "mix.v", "q_conv": "mix.q.conv", "k_conv": "mix.k.conv", "v_conv": "mix.v.conv",
+        "a": "mix.a", "b": "mix.b", "a_log": "mix.A_log", "dt_bias": "mix.dt_bias", "gate": "mix.g", "norm": "mix.norm",
+        "o": "mix.o"})
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Mixers side by side that read the same input: the result is `scale` times the sum of their outputs, each first
+    divided by its root mean square over the model's width (`eps`) and multiplied by a weight of its own
+    (`out_names[k]` for `branches[k]`). A branch is any mixer spec; each keeps what it keeps per sequence."""
+    hidden: int
+    branches: Tuple[object, ...]
+    out_names: Tuple[str, ...]
+    scale: float
+    eps: float
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
+class LearnedPositionEmbeddingSpec:
+    """Token embedding = table[tok] + rows[position]: a learned vector per position, `positions` of them."""
+    width: int
+    vocab: int
+    positions: int
+    names: Dict[str, str] = field(default_factory=lambda: {"table": "embed", "rows": "pos"})
+    kind: str = "learned_position"
 
 
 @dataclass(frozen=True)
@@ -232,6 +291,7 @@ class NormSpec:
     width: int
     eps: float
     kind: str = "rmsnorm"    # "layernorm": (x - mean) * (variance + eps)^(-1/2) * w, no bias (parts/layernorm.py)
+    offset: float = 0.0      # rmsnorm: the stored weight stands around zero and the norm multiplies by offset + w
 
 
 @dataclass(frozen=True)
@@ -265,7 +325,15 @@ class LayerSpec:
         "pre_mixer": "operator_norm.weight", "post_mixer": "post_operator_norm.weight",
         "pre_ffn": "ffn_norm.weight", "post_ffn": "post_ffn_norm.weight"})
     kind: str = "pre_norm"   # the arrangement (registry.register_arrangement); the formula above is "pre_norm";
-                             # "branch_norm": h += post(mixer(h)); h += post(ffn(h)), no norm before a sublayer
+                             # "branch_norm": h += post(mixer(h)); h += post(ffn(h)), no norm before a sublayer;
+                             # "gated_pre_norm": the pre-norm layer with the three options below (parts/block.py)
+    input_taps: int = 0      # > 0: a sublayer reads x + filter(x), a causal per-channel filter of so many taps over the
+                             # normed stream x (names "mixer_taps", "ffn_taps": [width, taps]); the last taps - 1 rows of
+                             # x are part of a sequence's state, for each sublayer
+    branch_gate: bool = False  # a sublayer's result joins the stream times sigmoid(x G^T + b) (names "mixer_gate",
+                             # "mixer_gate_bias", "ffn_gate", "ffn_gate_bias"), x the normed stream before the filter
+    depth_terms: int = 0     # n > 0: what the layer hands on is sum_j c[j] X_j over the embedding's output X_0 and the
+                             # results X_1 .. X_(n-1) of the layers so far, this one's last (names "depth": [n])
 
 
 @dataclass(frozen=True)
@@ -294,6 +362,7 @@ class ModelSpec:
     prefixes: Tuple[str, ...] = ("model.",)   # tried in turn for "<prefix>embed_tokens.weight"
     ignorable: Tuple[str, ...] = ()           # regular expressions: tensors of a folder that match are neither needed nor refused
     embedding: Optional[object] = None        # a spec with a `kind` (registry.register_embedding); None: table[tok] * embed_scale
+    depth_history: bool = False               # the step keeps every layer's result (layers with `depth_terms` read them)
     names: Dict[str, str] = field(default_factory=lambda: {
         "embed": "embed_tokens.weight", "final_norm": "embedding_norm.weight",
         "head": "lm_head.weight"})   # "head" is looked up without the model prefix

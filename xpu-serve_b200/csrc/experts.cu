@@ -228,6 +228,102 @@ __global__ void moe_route_warp_kernel(const float* __restrict__ logits, int ld, 
     }
 }
 
+// Routing by sigmoid scores with a limit on groups. A token's scores are s = sigmoid(logits); its choice scores c = s +
+// correction (a number per expert). The experts form `groups` equal groups of neighbours; a group's score is the sum of its
+// `group_top` largest choice scores, and only experts of the `keep` best groups can be chosen (the others count as minus
+// infinity, so negative choice scores still beat them). The `top` largest choice scores are chosen (ties: the lower index,
+// for groups and for experts); the weights are the chosen experts' s times `scale`, not normed to sum 1 unless `renorm`.
+// A warp per token; the token's s and c stand in shared memory (2 E floats a warp).
+__global__ void moe_route_grouped_kernel(const float* __restrict__ logits, int ld, int T, int E, int top,
+                                         const float* __restrict__ correction, int groups, int keep, int group_top, float scale,
+                                         int renorm, int32_t* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float route_smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* s = route_smem + (size_t)warp * (2 * E + groups);
+    float* c = s + E;
+    float* gs = c + E;
+    const float* z = logits + (int64_t)t * ld;
+    for (int e = lane; e < E; e += 32) {
+        const float v = 1.0f / (1.0f + expf(-z[e]));
+        s[e] = v;
+        c[e] = v + (correction != nullptr ? correction[e] : 0.0f);
+    }
+    __syncwarp();
+    const int per = E / groups;
+    if (groups > 1 && keep < groups) {
+        for (int g = lane; g < groups; g += 32) {
+            // the sum of the group's `group_top` largest choice scores: pick them one after another
+            float sum = 0.0f;
+            int taken[8];
+            const int n = min(group_top, per);
+            for (int k = 0; k < n; ++k) {
+                float bv = -INFINITY;
+                int bi = -1;
+                for (int j = 0; j < per; ++j) {
+                    bool used = false;
+                    for (int q = 0; q < k; ++q) used |= taken[q] == j;
+                    if (!used && (bi < 0 || c[g * per + j] > bv)) {
+                        bv = c[g * per + j];
+                        bi = j;
+                    }
+                }
+                taken[k] = bi;
+                sum += bv;
+            }
+            gs[g] = sum;
+        }
+        __syncwarp();
+        // groups that are not among the `keep` best: rank = how many groups beat this one (ties: the lower index wins)
+        for (int g = lane; g < groups; g += 32) {
+            int rank = 0;
+            for (int o = 0; o < groups; ++o) rank += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+            if (rank >= keep)
+                for (int j = 0; j < per; ++j) c[g * per + j] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    float mine = 0.0f, sum = 0.0f;
+    int mine_id = 0;
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int bi = 1 << 30;
+        for (int e = lane; e < E; e += 32) {
+            const float v = c[e];
+            if (v > bv || (v == bv && e < bi)) {
+                bv = v;
+                bi = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if (bi >= E) bi = 0;                    // (only a row of NaNs comes here)
+        const float w = s[bi];
+        __syncwarp();
+        if (lane == 0) c[bi] = -INFINITY;       // taken (enough experts are open, so none at minus infinity is ever chosen)
+        __syncwarp();
+        sum += w;
+        if (lane == k) {
+            mine = w;
+            mine_id = bi;
+        }
+    }
+    if (lane < top) {
+        ids[(int64_t)t * top + lane] = mine_id;
+        wts[(int64_t)t * top + lane] = (renorm ? mine / sum : mine) * scale;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------------------- plan
 // meta: [0] number of tiles; then per tile 3 words (expert, first row, rows) from meta[4] on.
 // pad: every expert's rows start at a multiple of tile_rows (places that no row takes get source -1; rows_cap places).
@@ -466,6 +562,23 @@ XS_API int xs_moe_route(const float* logits, int ld, int T, int E, int top, floa
     else
         xs_launch(moe_route_kernel, dim3(ceil_div_i(T, 32)), dim3(32), 0, stream, logits, ld, T, E, top, scale, ids, wts);
     XS_LAUNCH_CHECK("moe_route");
+    return 0;
+}
+
+XS_API int xs_moe_route_grouped(const float* logits, int ld, int T, int E, int top, const float* correction, int groups, int keep,
+                                int group_top, float scale, int renorm, int32_t* ids, float* wts, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop && ld >= E,
+               "moe_route_grouped: %d tokens, %d experts (row stride %d), top %d (at most %d)", T, E, ld, top, kMaxTop);
+    XS_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && group_top > 0 && group_top <= 8,
+               "moe_route_grouped: %d experts in %d groups of which %d are kept (a group's %d largest count)", E, groups, keep, group_top);
+    XS_REQUIRE((int64_t)keep * (E / groups) >= top, "moe_route_grouped: %d groups of %d experts cannot give %d choices", keep, E / groups, top);
+    const size_t per_warp = (size_t)(2 * E + groups) * sizeof(float);
+    XS_REQUIRE(per_warp <= 40 * 1024, "moe_route_grouped: %d experts are more than the kernel's shared memory holds", E);
+    const int warps = per_warp * 4 <= 40 * 1024 ? 4 : 1;
+    xs_launch(moe_route_grouped_kernel, dim3(ceil_div_i(T, warps)), dim3(32 * warps), per_warp * warps, stream, logits, ld, T, E, top,
+              correction, groups, keep, group_top, scale, renorm, ids, wts);
+    XS_LAUNCH_CHECK("moe_route_grouped");
     return 0;
 }
 

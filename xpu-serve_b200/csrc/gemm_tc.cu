@@ -984,7 +984,7 @@ XS_API int xs_gemm_tc_grouped(const void* x, const void* w, void* out, int out_d
     XS_REQUIRE(xs_gemm_tc_supports(rows_cap, N, K, ldx, K), "gemm (tcgen05, grouped): rows %d, N %d, K %d, stride %lld not supported",
                rows_cap, N, K, (long long)ldx);
     XS_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm (tcgen05, grouped): operands must be 16-byte aligned");
-    XS_REQUIRE((epilogue == EPI_STORE || epilogue == EPI_SWIGLU) && status != nullptr && out != nullptr && meta != nullptr,
+    XS_REQUIRE((epilogue == EPI_STORE || epilogue == EPI_SWIGLU || epilogue == EPI_RELU_SQ) && status != nullptr && out != nullptr && meta != nullptr,
                "gemm (tcgen05, grouped): bad arguments");
     XS_REQUIRE(epilogue != EPI_SWIGLU || N % 16 == 0, "gemm (tcgen05, grouped): the fused activation needs N %% 16 == 0");
     XS_REQUIRE(rows_cap >= max_m_tiles * BM && E > 0 && (int64_t)E * N < 2147483647, "gemm (tcgen05, grouped): %d rows for %d tiles",

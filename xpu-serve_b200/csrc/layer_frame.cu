@@ -1,0 +1,220 @@
+// Pieces of a layer's frame that are neither a product nor a mixer:
+//
+//   embed_pos          h[t] = table[id[t]] + rows[position[t]]: a token table plus a learned row per position
+//   causal_conv        y[t, c] = (x[t, c] if residual) + act(sum_j taps[c, j] x[t - (n - 1) + j, c]) over a sequence's earlier
+//                      tokens, the inputs before a step coming from the sequence's state [n - 1, C], which then moves on
+//   gated_add          h[t, c] += branch[t, c] * sigmoid(logit[t, c] + bias[c]): a branch joins the float32 stream through
+//                      a gate
+//   depth_average      out[t, c] = sum_j coef[j] * hist[j, t, c]: what a layer hands on as a weighted sum of the embedding's
+//                      and every earlier layer's results
+//   rmsnorm_accumulate acc[t, :] (+)= scale * x[t, :] / sqrt(mean(x[t, :]^2) + eps) * w: branches that run side by side are
+//                      normed and summed in float32
+//
+// All sums are float32 in a fixed order per element, whatever else is in the batch.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxTaps = 16;
+constexpr int kMaxTerms = 512;
+
+template <typename T>
+__global__ void embed_pos_kernel(const T* __restrict__ table, const T* __restrict__ rows, const int32_t* __restrict__ ids,
+                                 const int32_t* __restrict__ positions, float* __restrict__ h, int H) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int64_t id = ids[t], pos = positions[t];
+    pdl_wait();
+    const T* a = table + id * H;
+    const T* b = rows + pos * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) h[(int64_t)t * H + c] = to_f32(a[c]) + to_f32(b[c]);
+}
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+
+template <typename T>
+__global__ void causal_conv_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ taps_w,
+                                   const T* __restrict__ state, const int32_t* __restrict__ seq_of_token,
+                                   const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
+                                   T* __restrict__ out, int64_t ldo, int C, int taps, int act, int residual) {
+    pdl_launch_dependents();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x;
+    if (c >= C) return;
+    float w[kMaxTaps];
+    for (int k = 0; k < taps; ++k) w[k] = taps_w[(int64_t)c * taps + k];
+    const int seq = seq_of_token[t];
+    const int local = t - cu_seqlens[seq];
+    const int64_t slot = slots[seq];
+    pdl_wait();
+    float acc = 0.0f, cur = 0.0f;
+    for (int k = 0; k < taps; ++k) {
+        const int back = taps - 1 - k;
+        float v;
+        if (local - back >= 0)
+            v = to_f32(x[(int64_t)(t - back) * ldx + c]);
+        else      // state row n - 1 - j holds the input j positions before the step (j = back - local)
+            v = to_f32(state[(slot * (taps - 1) + (taps - 1 - (back - local))) * C + c]);
+        if (back == 0) cur = v;
+        acc = fmaf(w[k], v, acc);
+    }
+    if (act == 1) acc = silu_f(acc);
+    if (residual) acc += cur;
+    out[(int64_t)t * ldo + c] = from_f32<T>(acc);
+}
+
+// After the convolution: a sequence's state becomes its last n - 1 inputs (the step's, and the old state's where the step
+// brought fewer).
+template <typename T>
+__global__ void causal_conv_state_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ state,
+                                         const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots, int C,
+                                         int taps) {
+    pdl_launch_dependents();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int seq = blockIdx.x;
+    if (c >= C) return;
+    const int t0 = cu_seqlens[seq], n = cu_seqlens[seq + 1] - t0;
+    const int64_t slot = slots[seq];
+    pdl_wait();
+    if (n <= 0) return;
+    T* st = state + slot * (taps - 1) * C + c;
+    T keep[kMaxTaps];
+    for (int j = 0; j < taps - 1; ++j) {
+        const int local = n - (taps - 1) + j;       // the input that row j holds after the step
+        keep[j] = local >= 0 ? x[(int64_t)(t0 + local) * ldx + c] : st[(int64_t)(j + n) * C];
+    }
+    for (int j = 0; j < taps - 1; ++j) st[(int64_t)j * C] = keep[j];
+}
+
+template <typename TB>
+__global__ void gated_add_kernel(float* __restrict__ h, const TB* __restrict__ branch, const float* __restrict__ logits,
+                                 int64_t ld_logits, const float* __restrict__ bias, int64_t total, int W) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int64_t t = i / W;
+    const int c = (int)(i - t * W);
+    const float z = logits[t * ld_logits + c] + (bias != nullptr ? bias[c] : 0.0f);
+    h[i] += to_f32(branch[i]) / (1.0f + expf(-z));
+}
+
+__global__ void depth_average_kernel(const float* __restrict__ hist, int64_t plane, const float* __restrict__ coef, int terms,
+                                     float* __restrict__ out, int64_t total) {
+    __shared__ float cs[kMaxTerms];
+    pdl_launch_dependents();
+    for (int j = threadIdx.x; j < terms; j += blockDim.x) cs[j] = coef[j];
+    __syncthreads();
+    pdl_wait();
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= total) return;
+    if (i + 4 <= total && (plane & 3) == 0) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < terms; ++j) {
+            const float4 v = *reinterpret_cast<const float4*>(hist + (int64_t)j * plane + i);
+            acc.x = fmaf(cs[j], v.x, acc.x); acc.y = fmaf(cs[j], v.y, acc.y);
+            acc.z = fmaf(cs[j], v.z, acc.z); acc.w = fmaf(cs[j], v.w, acc.w);
+        }
+        *reinterpret_cast<float4*>(out + i) = acc;
+        return;
+    }
+    for (int64_t e = i; e < total && e < i + 4; ++e) {
+        float acc = 0.0f;
+        for (int j = 0; j < terms; ++j) acc = fmaf(cs[j], hist[(int64_t)j * plane + e], acc);
+        out[e] = acc;
+    }
+}
+
+// One block a row; the row's sum of squares in a fixed order (block_sum), then acc (+)= scale * x / rms * w.
+template <typename T>
+__global__ void rmsnorm_accumulate_kernel(const T* __restrict__ x, const float* __restrict__ w, float* __restrict__ acc, int W,
+                                          float eps, float scale, int add) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* xr = x + (int64_t)blockIdx.x * W;
+    float* ar = acc + (int64_t)blockIdx.x * W;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = to_f32(xr[c]);
+        ss = fmaf(v, v, ss);
+    }
+    const float inv = scale / sqrtf(block_sum(ss, scratch) / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = to_f32(xr[c]) * inv * w[c];
+        ar[c] = add ? ar[c] + v : v;
+    }
+}
+
+}  // namespace
+
+XS_API int xs_embed_pos(const void* table, const void* rows, int dtype, const int32_t* ids, const int32_t* positions, float* h,
+                        int T, int H, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && H > 0, "embed_pos: %d tokens of width %d", T, H);
+    XS_DISPATCH_DTYPE(dtype, TT, xs_launch(embed_pos_kernel<TT>, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, (const TT*)table,
+                                           (const TT*)rows, ids, positions, h, H));
+    XS_LAUNCH_CHECK("embed_pos");
+    return 0;
+}
+
+// x: [T, >= C] rows `ldx` apart; out likewise `ldo` apart; state: [*, taps - 1, C] in x's element type. act 0: none, 1: silu
+// of the filter's sum. residual 1: the token's own input is added behind the activation.
+XS_API int xs_causal_conv(const void* x, int64_t ldx, const float* taps_w, void* state, const int32_t* seq_of_token,
+                          const int32_t* cu_seqlens, const int32_t* slots, void* out, int64_t ldo, int T, int n_seqs, int C,
+                          int taps, int act, int residual, int dtype, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(C > 0 && taps >= 1 && taps <= kMaxTaps, "causal_conv: %d channels, %d taps (at most %d)", C, taps, kMaxTaps);
+    XS_REQUIRE(T > 0 && n_seqs > 0 && C <= 65535 * 128 && (act == 0 || act == 1), "causal_conv: %d tokens in %d sequences, %d channels",
+               T, n_seqs, C);
+    const int tiles = ceil_div_i(C, 128);
+    XS_DISPATCH_DTYPE(dtype, TT,
+                      xs_launch(causal_conv_kernel<TT>, dim3(T, tiles), dim3(128), 0, stream, (const TT*)x, ldx, taps_w,
+                                (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, ldo, C, taps, act, residual));
+    XS_LAUNCH_CHECK("causal_conv");
+    if (taps > 1) {
+        XS_DISPATCH_DTYPE(dtype, TT,
+                          xs_launch(causal_conv_state_kernel<TT>, dim3(n_seqs, tiles), dim3(128), 0, stream, (const TT*)x, ldx,
+                                    (TT*)state, cu_seqlens, slots, C, taps));
+        XS_LAUNCH_CHECK("causal_conv (state)");
+    }
+    return 0;
+}
+
+XS_API int xs_gated_add(float* h, const void* branch, int branch_dtype, const float* logits, int64_t ld_logits, const float* bias,
+                        int T, int W, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && W > 0 && ld_logits >= W, "gated_add: %d rows of %d, gate rows %lld apart", T, W, (long long)ld_logits);
+    const int64_t total = (int64_t)T * W;
+    XS_DISPATCH_DTYPE(branch_dtype, TB,
+                      xs_launch(gated_add_kernel<TB>, dim3(ceil_div_i(total, 256)), dim3(256), 0, stream, h, (const TB*)branch,
+                                logits, ld_logits, bias, total, W));
+    XS_LAUNCH_CHECK("gated_add");
+    return 0;
+}
+
+// hist: `terms` planes of `plane` floats each, of which the first `total` are summed into out.
+XS_API int xs_depth_average(const float* hist, int64_t plane, const float* coef, int terms, float* out, int64_t total,
+                            cudaStream_t stream) {
+    if (total == 0) return 0;
+    XS_REQUIRE(terms > 0 && terms <= kMaxTerms && total > 0 && plane >= total, "depth_average: %d terms (at most %d) of %lld",
+               terms, kMaxTerms, (long long)total);
+    XS_REQUIRE(((uintptr_t)hist % 16 == 0) && ((uintptr_t)out % 16 == 0), "depth_average: buffers must be 16-byte aligned");
+    xs_launch(depth_average_kernel, dim3(ceil_div_i(ceil_div_i(total, 4), 256)), dim3(256), 0, stream, hist, plane, coef, terms, out,
+              total);
+    XS_LAUNCH_CHECK("depth_average");
+    return 0;
+}
+
+XS_API int xs_rmsnorm_accumulate(const void* x, int dtype, const float* w, float* acc, int T, int W, float eps, float scale,
+                                 int add, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && W > 0, "rmsnorm_accumulate: %d rows of %d", T, W);
+    XS_DISPATCH_DTYPE(dtype, TT,
+                      xs_launch(rmsnorm_accumulate_kernel<TT>, dim3(T), dim3(W >= 2048 ? 256 : 128), 0, stream, (const TT*)x, w, acc,
+                                W, eps, scale, add));
+    XS_LAUNCH_CHECK("rmsnorm_accumulate");
+    return 0;
+}

@@ -172,10 +172,12 @@ __global__ void add_layernorm_vec_kernel(float* __restrict__ h, const TM* __rest
 
 // y[t, g, :] = x[t, g, :] / sqrt(mean(x[t, g, :]^2) + eps) * w[g, :]: a unit-RMS norm in `groups` equal parts of a
 // row (x float32, y in the activation type). One block per (row, part).
-// With `gate` (rows of the activation type, `ld_gate` apart): y is also multiplied by sigmoid(gate[t, g, :]).
+// With `gate` (rows of the activation type, `ld_gate` apart): y is also multiplied by sigmoid(gate[t, g, :]), or with
+// gate_act 1 by silu(gate[t, g, :]) = gate * sigmoid(gate).
 template <typename TY>
 __global__ void grouped_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
-                                       int width, int part, float eps, const TY* __restrict__ gate, int64_t ld_gate) {
+                                       int width, int part, float eps, const TY* __restrict__ gate, int64_t ld_gate,
+                                       int gate_act) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -187,8 +189,10 @@ __global__ void grouped_rmsnorm_kernel(const float* __restrict__ x, const float*
     const float* wr = w + (int64_t)blockIdx.y * part;
     if (gate != nullptr) {
         const TY* gr = gate + (int64_t)blockIdx.x * ld_gate + (int64_t)blockIdx.y * part;
-        for (int c = threadIdx.x; c < part; c += blockDim.x)
-            y[base + c] = from_f32<TY>(xr[c] * inv * wr[c] / (1.0f + expf(-to_f32(gr[c]))));
+        for (int c = threadIdx.x; c < part; c += blockDim.x) {
+            const float gv = to_f32(gr[c]);
+            y[base + c] = from_f32<TY>(xr[c] * inv * wr[c] * (gate_act == 1 ? gv : 1.0f) / (1.0f + expf(-gv)));
+        }
         return;
     }
     for (int c = threadIdx.x; c < part; c += blockDim.x) y[base + c] = from_f32<TY>(xr[c] * inv * wr[c]);
@@ -199,7 +203,7 @@ __global__ void grouped_rmsnorm_kernel(const float* __restrict__ x, const float*
 template <typename TY>
 __global__ void grouped_rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
                                             int width, int part, int groups, float eps, const TY* __restrict__ gate,
-                                            int64_t ld_gate) {
+                                            int64_t ld_gate, int gate_act) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -224,7 +228,10 @@ __global__ void grouped_rmsnorm_warp_kernel(const float* __restrict__ x, const f
             const int c = lane + 32 * k;
             if (c < part) {
                 float o = v[k] * inv * wr[c];
-                if (gr != nullptr) o /= 1.0f + expf(-to_f32(gr[c]));
+                if (gr != nullptr) {
+                    const float gv = to_f32(gr[c]);
+                    o *= (gate_act == 1 ? gv : 1.0f) / (1.0f + expf(-gv));
+                }
                 y[base + c] = from_f32<TY>(o);
             }
             if (32 * (k + 1) >= part) break;
@@ -279,8 +286,9 @@ XS_API int xs_add_layernorm(float* h, const void* m, int m_dtype, const float* p
 }
 
 XS_API int xs_grouped_rmsnorm(const float* x, const float* w, void* y, int y_dtype, int rows, int width, int groups,
-                              float eps, const void* gate, int64_t ld_gate, cudaStream_t stream) {
+                              float eps, const void* gate, int64_t ld_gate, int gate_act, cudaStream_t stream) {
     if (rows == 0) return 0;
+    XS_REQUIRE(gate_act == 0 || gate_act == 1, "grouped_rmsnorm: gate activation %d (0 sigmoid, 1 silu)", gate_act);
     XS_REQUIRE(rows > 0 && width > 0 && groups > 0 && width % groups == 0, "grouped_rmsnorm: %d rows of %d in %d parts",
                rows, width, groups);
     XS_REQUIRE(groups <= 65535, "grouped_rmsnorm: %d parts exceed the grid limit", groups);
@@ -289,14 +297,14 @@ XS_API int xs_grouped_rmsnorm(const float* x, const float* w, void* y, int y_dty
         const int warps = groups < 8 ? groups : 8;
         XS_DISPATCH_DTYPE(y_dtype, TY,
                           xs_launch(grouped_rmsnorm_warp_kernel<TY>, dim3(rows), dim3(32 * warps), 0, stream, x, w, (TY*)y, width,
-                                    part, groups, eps, (const TY*)gate, ld_gate));
+                                    part, groups, eps, (const TY*)gate, ld_gate, gate_act));
         XS_LAUNCH_CHECK("grouped_rmsnorm");
         return 0;
     }
     const int threads = part >= 1024 ? 256 : 128;
     XS_DISPATCH_DTYPE(y_dtype, TY,
                       xs_launch(grouped_rmsnorm_kernel<TY>, dim3(rows, groups), dim3(threads), 0, stream, x, w, (TY*)y,
-                                width, part, eps, (const TY*)gate, ld_gate));
+                                width, part, eps, (const TY*)gate, ld_gate, gate_act));
     XS_LAUNCH_CHECK("grouped_rmsnorm");
     return 0;
 }

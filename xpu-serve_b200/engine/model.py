@@ -377,6 +377,10 @@ class Model:
         else:
             ops.embed(self.embed, ctx.tokens, h, spec.embed_scale)
         stream = ResidualStream(h, rt)
+        if spec.depth_history:
+            # every layer's result is kept for the layers that hand on a weighted sum of them (parts/block.py); the stream
+            # then lives in the history's planes, one further per layer, and one more takes the last layer's sum
+            stream.keep_history(rt.ws.get("depth_history", (len(spec.order) + 2, ctx.n_tokens, spec.hidden), torch.float32))
         last = len(spec.order) - 1
         for i, call in enumerate(spec.order):
             # the norm that reads the stream after this block, for products that carry the norm with them

@@ -54,7 +54,7 @@ def _signatures(lib) -> None:
         "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
         "xs_note_tokens": [P, P, I, I, P, P, I, P],
         "xs_add_layernorm": [P, P, I, P, P, P, I, P, I, I, F, F, P],
-        "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P, L, P],
+        "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P, L, I, P],
         "xs_clamped_glu": [P, P, I, I, I, L, F, F, F, I, P],
         "xs_gemm_tc_clamped": [P, P, P, I, I, I, I, L, L, L, F, F, F, P, P],
         "xs_moe_route": [P, I, I, I, I, F, P, P, P],
@@ -72,6 +72,13 @@ def _signatures(lib) -> None:
         "xs_gemm_batched": [P, L, L, P, L, L, P, L, L, I, I, I, I, I, P],
         "xs_latent_attention_mma": [P, L, L, P, P, P, I, P, P, P, L, P, P, L, L, P, L, I, I, I, I, I, I, I, F, I, I, P],
         "xs_mamba2_conv": [P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P],
+        "xs_embed_pos": [P, P, I, P, P, P, I, I, P],
+        "xs_causal_conv": [P, L, P, P, P, P, P, P, L, I, I, I, I, I, I, I, P],
+        "xs_gated_add": [P, P, I, P, L, P, I, I, P],
+        "xs_depth_average": [P, L, P, I, P, L, P],
+        "xs_rmsnorm_accumulate": [P, I, P, P, I, I, F, F, I, P],
+        "xs_gated_delta_scan": [P, L, I, I, I, P, L, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+        "xs_moe_route_grouped": [P, I, I, I, I, P, I, I, I, F, I, P, P, P],
         "xs_mamba2_scan": [P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_mamba2_scan_chunked": [P, P, L, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     }
@@ -795,16 +802,20 @@ def add_layernorm(h: torch.Tensor, m: Optional[torch.Tensor], post_w: Optional[t
 
 
 def grouped_rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, groups: int, eps: float,
-                    gate: Optional[torch.Tensor] = None) -> None:
+                    gate: Optional[torch.Tensor] = None, gate_act: str = "sigmoid") -> None:
     """y[t, g] = x[t, g] / sqrt(mean(x[t, g]^2) + eps) * w[g] for the `groups` equal parts g of a row; x float32.
-    `gate` (y's element type, rows at least as wide as x's, contiguous columns): y is also multiplied by sigmoid(gate)."""
+    `gate` (y's element type, rows at least as wide as x's, contiguous columns): y is also multiplied by sigmoid(gate),
+    or by silu(gate) with gate_act "silu"."""
+    if gate_act not in ("sigmoid", "silu"):
+        raise KernelError(f"grouped_rmsnorm: gate activation '{gate_act}' (sigmoid, silu)")
     _need(x, "x", torch.float32); _need(w, "w", torch.float32); _need(y, "y")
     if y.shape != x.shape or w.numel() != x.shape[1]:
         raise KernelError(f"grouped_rmsnorm: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     if gate is not None and (gate.dtype != y.dtype or gate.stride(1) != 1 or gate.shape[0] != x.shape[0] or gate.shape[1] < x.shape[1]):
         raise KernelError(f"grouped_rmsnorm: gate {tuple(gate.shape)} {gate.dtype} for y {tuple(y.shape)} {y.dtype}")
     _check(load().xs_grouped_rmsnorm(x.data_ptr(), w.data_ptr(), y.data_ptr(), _code(y), x.shape[0], x.shape[1],
-                                     int(groups), float(eps), _ptr(gate), 0 if gate is None else gate.stride(0), _stream()))
+                                     int(groups), float(eps), _ptr(gate), 0 if gate is None else gate.stride(0),
+                                     1 if gate_act == "silu" else 0, _stream()))
 
 
 def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float, interleave: int = 0) -> None:
@@ -864,6 +875,26 @@ def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tens
     _check(load().xs_moe_route(logits.data_ptr(), ld, T, E, int(top), float(scale), ids.data_ptr(), wts.data_ptr(), _stream()))
 
 
+def moe_route_grouped(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor, experts: Optional[int] = None,
+                      correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1, group_top: int = 2,
+                      scale: float = 1.0, renorm: bool = False) -> None:
+    """Per row of float32 logits: scores s = sigmoid(logit), choice scores c = s + correction; the experts stand in
+    `groups` equal groups of neighbours, of which the `keep` with the largest sum of their `group_top` largest choice
+    scores stay open; the `top` open experts with the largest c (ties: the lower index) go into ids, their s (times
+    `scale`; divided by their sum with `renorm`) into wts."""
+    _need(logits, "router logits", torch.float32); _need(ids, "ids", torch.int32); _need(wts, "weights", torch.float32)
+    T, ld = logits.shape
+    E = ld if experts is None else int(experts)
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+        if correction.numel() != E:
+            raise KernelError(f"moe_route_grouped: a correction of {correction.numel()} entries for {E} experts")
+    if ids.numel() < T * top or wts.numel() < T * top:
+        raise KernelError(f"moe_route_grouped: {T} tokens x top {top} do not fit ids {ids.numel()} / weights {wts.numel()}")
+    _check(load().xs_moe_route_grouped(logits.data_ptr(), ld, T, E, int(top), _ptr(correction), int(groups), int(keep),
+                                       int(group_top), float(scale), 1 if renorm else 0, ids.data_ptr(), wts.data_ptr(), _stream()))
+
+
 def moe_max_tiles_of(rows: int, experts: int, tile_rows: int) -> int:
     """The same for tiles of `tile_rows` rows with every expert's rows padded to whole tiles."""
     return int(load().xs_moe_max_tiles_of(rows, experts, tile_rows))
@@ -894,18 +925,22 @@ def moe_gather(x: torch.Tensor, source: torch.Tensor, top: int, sorted_rows: tor
 
 
 def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor, max_tiles: int, glu: bool,
-                    clamp=None) -> None:
+                    clamp=None, relu_squared: bool = False) -> None:
     """out[r] = w[expert of r's tile] . x[r] on tcgen05 tensor cores for the padded row tiles (128 rows) of a plan.
     w: [experts, N, K] bfloat16; with `glu` each expert's rows come in blocks of 8 gate and 8 up rows and
     out[r] = silu(gate) * up has N / 2 columns; `clamp` (limit, alpha, shift): the clamped unit's activation instead,
-    g * sigmoid(alpha g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    g * sigmoid(alpha g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit). `relu_squared` (without
+    `glu`): out[r] = max(product, 0)^2."""
     limit, alpha, shift = (0.0, 1.0, 0.0) if clamp is None else clamp
+    if glu and relu_squared:
+        raise KernelError("gemm (tcgen05, grouped): one activation at a time")
     _need(x, "x", torch.bfloat16); _need(w, "expert weights", torch.bfloat16); _need(out, "out", torch.bfloat16)
     E, N, K = w.shape
     if x.shape[1] != K or out.shape[0] != x.shape[0] or out.shape[1] != (N // 2 if glu else N) or x.shape[0] < 128 * max_tiles:
         raise KernelError(f"gemm (tcgen05, grouped): x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     mark_bounded(x.device)
-    _check(load().xs_gemm_tc_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), EPI_SWIGLU if glu else EPI_STORE,
+    _check(load().xs_gemm_tc_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out),
+                                     EPI_SWIGLU if glu else EPI_RELU_SQ if relu_squared else EPI_STORE,
                                      meta.data_ptr(), int(max_tiles), x.shape[0], E, N, K, x.stride(0), out.stride(0),
                                      float(limit), float(alpha), float(shift), gemm_tc_status(x.device).data_ptr(), _stream()))
 
@@ -1187,3 +1222,92 @@ def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: tor
                                          slots.data_ptr(), y.data_ptr(), chunk_state.data_ptr(), chunk_decay.data_ptr(),
                                          chunk_seq.data_ptr(), first_chunk.data_ptr(), n, n_seqs, heads, vdim, n_state,
                                          groups, _code(proj), _stream()), kernels=3)
+
+
+# ------------------------------------------------------------------------- a layer's frame
+def embed_pos(table: torch.Tensor, rows: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, h: torch.Tensor) -> None:
+    """h[t] = table[ids[t]] + rows[positions[t]], float32."""
+    _need(table, "embedding table"); _need(rows, "position rows", table.dtype); _need(ids, "ids", torch.int32)
+    _need(positions, "positions", torch.int32); _need(h, "h", torch.float32)
+    T, H = h.shape
+    if table.shape[1] != H or rows.shape[1] != H:
+        raise KernelError(f"embed_pos: table {tuple(table.shape)}, rows {tuple(rows.shape)}, h {tuple(h.shape)}")
+    _check(load().xs_embed_pos(table.data_ptr(), rows.data_ptr(), _code(table), ids.data_ptr(), positions.data_ptr(),
+                               h.data_ptr(), T, H, _stream()))
+
+
+def causal_conv(x: torch.Tensor, taps_w: torch.Tensor, state: torch.Tensor, seq_of_token: torch.Tensor,
+                cu_seqlens: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, act: str = "none",
+                residual: bool = False) -> None:
+    """out[t, c] = (x[t, c] with `residual`) + act(sum_j taps_w[c, j] * x[t - (n - 1) + j, c]) within each sequence, the
+    inputs before the step from `state` [*, n - 1, C] (x's element type), which is then moved on. act: "none" | "silu"."""
+    if act not in ("none", "silu"):
+        raise KernelError(f"causal_conv: activation '{act}' (none, silu)")
+    _need(taps_w, "taps", torch.float32); _need(state, "state", x.dtype)
+    T, C = out.shape
+    taps = taps_w.shape[1]
+    if (x.dim() != 2 or x.stride(1) != 1 or out.stride(1) != 1 or out.dtype != x.dtype or x.shape[0] != T or x.shape[1] < C
+            or taps_w.shape[0] != C):
+        raise KernelError(f"causal_conv: x {tuple(x.shape)}, taps {tuple(taps_w.shape)}, out {tuple(out.shape)}")
+    if taps > 1 and tuple(state.shape[1:]) != (taps - 1, C):
+        raise KernelError(f"causal_conv: state is {tuple(state.shape)}, expected [*, {taps - 1}, {C}]")
+    _check(load().xs_causal_conv(x.data_ptr(), x.stride(0), taps_w.data_ptr(), state.data_ptr(), seq_of_token.data_ptr(),
+                                 cu_seqlens.data_ptr(), slots.data_ptr(), out.data_ptr(), out.stride(0), T, slots.numel(), C,
+                                 taps, 1 if act == "silu" else 0, 1 if residual else 0, _code(x), _stream()),
+           kernels=2 if taps > 1 else 1)
+
+
+def gated_add(h: torch.Tensor, branch: torch.Tensor, logits: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+    """h += branch * sigmoid(logits + bias): h float32 [T, W]; logits float32 rows at least W wide."""
+    _need(h, "h", torch.float32); _need(branch, "branch")
+    T, W = h.shape
+    if tuple(branch.shape) != (T, W) or logits.dtype != torch.float32 or logits.shape[0] != T or logits.shape[1] < W or logits.stride(1) != 1:
+        raise KernelError(f"gated_add: h {tuple(h.shape)}, branch {tuple(branch.shape)}, gate {tuple(logits.shape)} {logits.dtype}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != W:
+            raise KernelError(f"gated_add: a bias of {bias.numel()} entries for rows of {W}")
+    _check(load().xs_gated_add(h.data_ptr(), branch.data_ptr(), _code(branch), logits.data_ptr(), logits.stride(0), _ptr(bias),
+                               T, W, _stream()))
+
+
+def depth_average(history: torch.Tensor, coef: torch.Tensor, terms: int, out: torch.Tensor) -> None:
+    """out = sum over j < terms of coef[j] * history[j]; history [n, T, W] float32, out [T, W] float32 (it may be a later
+    plane of `history`)."""
+    _need(history, "history", torch.float32); _need(coef, "coefficients", torch.float32); _need(out, "out", torch.float32)
+    if history.dim() != 3 or history.shape[0] < terms or coef.numel() != terms or out.shape != history.shape[1:]:
+        raise KernelError(f"depth_average: history {tuple(history.shape)}, {coef.numel()} coefficients for {terms} terms, "
+                          f"out {tuple(out.shape)}")
+    _check(load().xs_depth_average(history.data_ptr(), history.stride(0), coef.data_ptr(), int(terms), out.data_ptr(),
+                                   out.numel(), _stream()))
+
+
+def rmsnorm_accumulate(x: torch.Tensor, w: torch.Tensor, acc: torch.Tensor, eps: float, scale: float, add: bool) -> None:
+    """acc = (acc if add else 0) + scale * x / sqrt(mean(x^2) + eps) * w, row by row, float32."""
+    _need(x, "x"); _need(w, "w", torch.float32); _need(acc, "acc", torch.float32)
+    T, W = x.shape
+    if tuple(acc.shape) != (T, W) or w.numel() != W:
+        raise KernelError(f"rmsnorm_accumulate: x {tuple(x.shape)}, w {tuple(w.shape)}, acc {tuple(acc.shape)}")
+    _check(load().xs_rmsnorm_accumulate(x.data_ptr(), _code(x), w.data_ptr(), acc.data_ptr(), T, W, float(eps), float(scale),
+                                        1 if add else 0, _stream()))
+
+
+def gated_delta_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, ab: torch.Tensor, a_log: torch.Tensor,
+                     dt_bias: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, y: torch.Tensor,
+                     heads: int, key_heads: int, dim: int, vdim: int, q_scale: float, unit_eps: float) -> None:
+    """The gated delta rule over a step's tokens (csrc/gated_delta.cu). qkv: rows with q (key_heads * dim), k (likewise) and
+    v (heads * vdim) from the given columns on; ab float32 rows [a: heads | b: heads | ...]; state [*, heads, dim, vdim]
+    float32; y [T, heads * vdim] float32."""
+    _need(ab, "gate inputs", torch.float32); _need(state, "state", torch.float32); _need(y, "y", torch.float32)
+    _need(a_log, "A_log", torch.float32); _need(dt_bias, "dt_bias", torch.float32)
+    T = y.shape[0]
+    if (qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[0] != T or ab.shape[0] != T or ab.shape[1] < 2 * heads
+            or y.shape[1] != heads * vdim or a_log.numel() != heads or dt_bias.numel() != heads
+            or max(q_col, k_col) + key_heads * dim > qkv.shape[1] or v_col + heads * vdim > qkv.shape[1]):
+        raise KernelError(f"gated_delta_scan: qkv {tuple(qkv.shape)}, gates {tuple(ab.shape)}, y {tuple(y.shape)}")
+    if tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError(f"gated_delta_scan: state is {tuple(state.shape)}, expected [*, {heads}, {dim}, {vdim}]")
+    _check(load().xs_gated_delta_scan(qkv.data_ptr(), qkv.stride(0), int(q_col), int(k_col), int(v_col), ab.data_ptr(),
+                                      ab.stride(0), a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(),
+                                      cu_seqlens.data_ptr(), slots.data_ptr(), y.data_ptr(), slots.numel(), int(heads),
+                                      int(key_heads), int(dim), int(vdim), float(q_scale), float(unit_eps), _code(qkv), _stream()))

@@ -10,10 +10,13 @@ from .latent_attention import LatentAttentionMixer
 from .mamba2 import Mamba2Mixer
 from .gated_units import ClampedGLU, RoutedExperts, SquaredRelu
 from .mlstm import MLstmMixer
-from .embedding import PairHashEmbedding
-from .block import Block, BranchNormBlock, ResidualStream
+from .gated_delta import GatedDeltaMixer
+from .parallel import ParallelMixer
+from .embedding import LearnedPositionEmbedding, PairHashEmbedding
+from .block import Block, BranchNormBlock, GatedPreNormBlock, ResidualStream
 
 __all__ = ["FeedForward", "KVNeed", "Mixer", "Norm", "RMSNorm", "Part", "StateNeed", "TensorSpec", "RotaryTable",
            "AttentionMixer", "ShortConvMixer", "SwiGLU", "Block", "ResidualStream", "LayerNorm", "ScaledRotaryTable",
            "LatentAttentionMixer", "Mamba2Mixer", "ClampedGLU", "RoutedExperts", "SquaredRelu", "MLstmMixer",
-           "PairHashEmbedding", "BranchNormBlock"]
+           "PairHashEmbedding", "BranchNormBlock", "GatedDeltaMixer", "ParallelMixer", "LearnedPositionEmbedding",
+           "GatedPreNormBlock"]

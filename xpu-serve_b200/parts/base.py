@@ -108,7 +108,9 @@ class Norm(Part):
 
     @classmethod
     def tensors(cls, spec, weight_name: str) -> Dict[str, TensorSpec]:
-        return {weight_name: TensorSpec((spec.width,), init="ones", role="vector")}
+        # (a weight that the norm uses as offset + w stands around zero)
+        init = "uniform:-0.3:0.3" if getattr(spec, "offset", 0.0) else "ones"
+        return {weight_name: TensorSpec((spec.width,), init=init, role="vector")}
 
     def __init__(self, spec, weights, weight_name: str, rt):
         self.spec, self.rt = spec, rt

@@ -28,7 +28,8 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from .. import registry
-from .base import Norm, TensorSpec
+from ..ops import lib as ops
+from .base import Norm, StateNeed, TensorSpec
 
 
 class Prenormed:
@@ -79,6 +80,32 @@ class ResidualStream:
         self._pre = None          # (norm weight, stream * weight, sums of squares) left by the last fused product
         self._flip = 0
         self._plain_add: Optional[Norm] = None
+        self.history: Optional[torch.Tensor] = None     # [results kept + 2, tokens, width] float32 (`keep_history`)
+        self.recorded = 0                               # planes of `history` that hold a finished result
+
+    def keep_history(self, history: torch.Tensor) -> None:
+        """From now on the stream keeps every layer's result. `history[0]` is the embedding's output, which the stream
+        holds now; the stream moves to plane 1 (a copy), where the first layer turns it into its result."""
+        self.flush()
+        if history[0].data_ptr() != self.h.data_ptr():
+            history[0].copy_(self.h)
+        history[1].copy_(history[0])
+        self.history, self.recorded, self.h = history, 1, history[1]
+        self._pre = None
+
+    def depth_average(self, coef: torch.Tensor, terms: int) -> None:
+        """The layer that ends here has turned the stream into its result, plane `terms - 1` of the history. What the next
+        layer (or the head) reads is sum_j coef[j] * history[j] over the `terms` results so far: it goes into the next
+        plane, where the next layer works in place, so no result is ever copied."""
+        if self.history is None:
+            raise RuntimeError("a layer averages over earlier results, but the step keeps none (ModelSpec.depth_history)")
+        if terms != self.recorded + 1 or terms + 1 > self.history.shape[0] or self.h.data_ptr() != self.history[terms - 1].data_ptr():
+            raise RuntimeError(f"a layer averages over {terms} results where {self.recorded + 1} exist")
+        self.flush()
+        nxt = self.history[terms]
+        ops.depth_average(self.history, coef, terms, nxt)
+        self.h, self.recorded = nxt, terms
+        self._pre = None
 
     def add(self, branch: torch.Tensor, post: Optional[Norm] = None) -> None:
         if self._pending is not None:
@@ -244,5 +271,106 @@ class BranchNormBlock:
             stream.add(self.ffn.forward(y, step), self.post_ffn)
 
 
+def _needs_of(need) -> tuple:
+    return () if need is None else tuple(need) if isinstance(need, (tuple, list)) else (need,)
+
+
+class GatedPreNormBlock:
+    """The pre-norm layer with three options, each a field of the layer's spec:
+
+        a = norm1(h);  h += G1(a) * mixer(F1(a))        F(a) = a + filter(a)   (`input_taps`; identity without)
+        f = norm2(h);  h += G2(f) * ffn(F2(f))          G(a) = sigmoid(a G^T + b)   (`branch_gate`; 1 without)
+        h <- sum_j c[j] X_j                             (`depth_terms`: X_0 the embedding's output, X_j layer j - 1's h)
+
+    The filter is causal and per channel over a sequence's earlier tokens; its last taps - 1 inputs are part of the
+    sequence's state (one need per sublayer, behind the mixer's own). Gate logits and the sum with the gated branch are
+    float32."""
+    kind = "gated_pre_norm"
+    fixed_shape_ok = True
+
+    @classmethod
+    def tensors(cls, layer) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        n, W = layer.names, layer.norm.width
+        norm_cls = registry.norm_class(layer.norm.kind)
+        subs = ["mixer"] + (["ffn"] if layer.ffn is not None else [])
+        for sub in subs:
+            out.update(norm_cls.tensors(layer.norm, n[f"pre_{sub}"]))
+        out.update(registry.mixer_class(layer.mixer.kind).tensors(layer.mixer))
+        if layer.ffn is not None:
+            out.update(registry.ffn_class(layer.ffn.kind).tensors(layer.ffn))
+        for sub in subs:
+            if layer.input_taps > 0:
+                out[n[f"{sub}_taps"]] = TensorSpec((W, layer.input_taps), init="uniform:-0.3:0.3", role="vector")
+            if layer.branch_gate:
+                out[n[f"{sub}_gate"]] = TensorSpec((W, W))
+                out[n[f"{sub}_gate_bias"]] = TensorSpec((W,), init="uniform:-1:1", role="vector")
+        if layer.depth_terms > 0:
+            out[n["depth"]] = TensorSpec((layer.depth_terms,), init="uniform:0.1:0.6", role="vector")
+        return out
+
+    @classmethod
+    def cache_need(cls, layer):
+        needs = _needs_of(registry.mixer_class(layer.mixer.kind).cache_need(layer.mixer))
+        if layer.input_taps > 1:
+            rows = StateNeed((layer.input_taps - 1, layer.norm.width), "compute")
+            needs = needs + (rows,) * (2 if layer.ffn is not None else 1)
+        return needs if needs else None
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+        if spec.sandwich:
+            raise ValueError("gated_pre_norm: a layer with sandwich norms is the plain pre_norm arrangement's")
+        if not 0 <= spec.input_taps <= 16:
+            raise ValueError(f"gated_pre_norm: {spec.input_taps} taps (at most 16 are supported)")
+        self.spec, self.rt = spec, rt
+        self.mixer = registry.mixer_class(spec.mixer.kind)(spec.mixer, weights, rt)
+        self.ffn = registry.ffn_class(spec.ffn.kind)(spec.ffn, weights, rt) if spec.ffn is not None else None
+        n = spec.names
+        norm_cls = registry.norm_class(spec.norm.kind)
+        self.pre_mixer = norm_cls(spec.norm, weights, n["pre_mixer"], rt)
+        self.pre_ffn = norm_cls(spec.norm, weights, n["pre_ffn"], rt) if self.ffn is not None else None
+        self.first_norm = None                # (the stream is rewritten between layers: nothing is prepared across them)
+        self.mixer_needs = len(_needs_of(registry.mixer_class(spec.mixer.kind).cache_need(spec.mixer)))
+        self.taps, self.gates = {}, {}
+        for sub in ["mixer"] + (["ffn"] if self.ffn is not None else []):
+            if spec.input_taps > 0:
+                self.taps[sub] = rt.vector(weights[n[f"{sub}_taps"]].reshape(spec.norm.width, spec.input_taps))
+            if spec.branch_gate:
+                self.gates[sub] = (rt.matrix(weights[n[f"{sub}_gate"]]), rt.vector(weights[n[f"{sub}_gate_bias"]]))
+        self.depth = rt.vector(weights[n["depth"]]) if spec.depth_terms > 0 else None
+
+    def _sublayer(self, sub: str, stream: ResidualStream, norm: Norm, step, cache, rows_view, run) -> None:
+        rt = self.rt
+        a = stream.norm(norm)
+        logits = None
+        if sub in self.gates:
+            logits = rt.linear(a, self.gates[sub][0], "branch_gate", out_dtype=torch.float32)
+        x = a
+        if sub in self.taps:
+            x = rt.ws.get("filtered_input", tuple(a.shape), a.dtype)
+            state = rows_view.storage if rows_view is not None else a      # (one tap keeps nothing)
+            ops.causal_conv(a, self.taps[sub], state, step.seq_of_token, step.cu_seqlens, step.slots, x, residual=True)
+        branch = run(x)
+        if logits is None:
+            stream.add(branch)
+        else:
+            ops.gated_add(stream.h, branch, logits, self.gates[sub][1])
+
+    def forward(self, stream: ResidualStream, step, cache, next_norm: Optional[Norm] = None) -> None:
+        k = self.mixer_needs
+        keeps_rows = self.spec.input_taps > 1
+        if keeps_rows and (cache is None or len(cache) < k + (2 if self.ffn is not None else 1)):
+            raise RuntimeError("gated_pre_norm: the layer keeps its filters' last inputs per sequence")
+        mixer_cache = cache.sub(0, k) if cache is not None else None
+        self._sublayer("mixer", stream, self.pre_mixer, step, cache, cache[k] if keeps_rows else None,
+                       lambda x: self.mixer.forward(x, step, mixer_cache))
+        if self.ffn is not None:
+            self._sublayer("ffn", stream, self.pre_ffn, step, cache, cache[k + 1] if keeps_rows else None,
+                           lambda y: self.ffn.forward(y, step))
+        if self.depth is not None:
+            stream.depth_average(self.depth, self.spec.depth_terms)
+
+
 registry.register_arrangement(Block.kind, Block)
+registry.register_arrangement(GatedPreNormBlock.kind, GatedPreNormBlock)
 registry.register_arrangement(BranchNormBlock.kind, BranchNormBlock)

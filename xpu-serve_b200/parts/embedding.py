@@ -56,4 +56,31 @@ class PairHashEmbedding(Part):
                        cache.storage, self.inv_freq, self.w_norm, h, s.scale, s.buckets, s.mul_prev, s.mul_cur, s.eps)
 
 
+class LearnedPositionEmbedding(Part):
+    """table[tok] + rows[position]: a learned vector per position joins the token's (csrc/layer_frame.cu: xs_embed_pos).
+    Nothing is kept per sequence; a sequence cannot outgrow the rows (the model's `max_position` bounds the cache)."""
+    kind = "learned_position"
+    fixed_shape_ok = True
+
+    @classmethod
+    def tensors(cls, spec) -> Dict[str, TensorSpec]:
+        return {spec.names["rows"]: TensorSpec((spec.positions, spec.width))}
+
+    @classmethod
+    def cache_need(cls, spec):
+        return None
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt, table: torch.Tensor):
+        if spec.positions <= 0:
+            raise ValueError("learned positions: the table needs at least one row")
+        self.spec, self.rt, self.table = spec, rt, table
+        self.rows = rt.matrix(weights[spec.names["rows"]])
+
+    def forward(self, step, cache, h: torch.Tensor) -> None:
+        if step.max_positions > self.spec.positions:
+            raise RuntimeError(f"learned positions: the cache allows {step.max_positions} positions, the table has {self.spec.positions}")
+        ops.embed_pos(self.table, self.rows, step.tokens, step.positions, h)
+
+
 registry.register_embedding(PairHashEmbedding.kind, PairHashEmbedding)
+registry.register_embedding(LearnedPositionEmbedding.kind, LearnedPositionEmbedding)

@@ -9,6 +9,9 @@ RoutedExperts:  `experts` gated feed-forwards without biases (SwiGLU, or clamped
                 (csrc/experts.cu); no count ever reaches the host, so a step with experts can be captured in a graph.
                 With `shared`, a clamped unit that every token uses joins the sum, times the sigmoid of one more
                 logit a token (its one-row matrix is the router's last row here, so the router product gives both).
+                `score` "sigmoid": scores sigmoid(logit); chosen by score plus a correction per expert among the best
+                groups of neighbouring experts, weighted by the scores as they are (config/spec.py: RoutedExpertsSpec).
+                `activation` "relu_squared": an expert is down(max(up x, 0)^2).
 """
 from __future__ import annotations
 
@@ -98,10 +101,13 @@ class RoutedExperts(FeedForward):
         n = spec.names
         out = {}
         for e in range(spec.experts):
-            out[n["gate"].format(e=e)] = TensorSpec((spec.intermediate, spec.hidden))
+            if spec.activation == "gated":
+                out[n["gate"].format(e=e)] = TensorSpec((spec.intermediate, spec.hidden))
             out[n["up"].format(e=e)] = TensorSpec((spec.intermediate, spec.hidden))
             out[n["down"].format(e=e)] = TensorSpec((spec.hidden, spec.intermediate))
         out[n["router"]] = TensorSpec((spec.experts, spec.hidden))
+        if spec.correction:
+            out[n["correction"]] = TensorSpec((spec.experts,), init="uniform:-0.3:0.3", role="vector")
         if spec.shared is not None:
             out.update(ClampedGLU.tensors(spec.shared))
             out[n["shared_gate"]] = TensorSpec((1, spec.hidden))
@@ -110,7 +116,16 @@ class RoutedExperts(FeedForward):
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
         if spec.top > 16:
             raise ValueError(f"routed experts: top {spec.top} (at most 16 are supported)")
+        if spec.score not in ("softmax", "sigmoid") or spec.activation not in ("gated", "relu_squared"):
+            raise ValueError(f"routed experts: score '{spec.score}' (softmax, sigmoid), activation '{spec.activation}' (gated, relu_squared)")
+        if spec.score == "softmax" and (spec.correction or spec.groups != 1):
+            raise ValueError("routed experts: a correction and groups belong to sigmoid scores")
+        if spec.groups < 1 or spec.experts % spec.groups != 0 or not 1 <= spec.keep_groups <= spec.groups \
+                or spec.keep_groups * (spec.experts // spec.groups) < spec.top:
+            raise ValueError(f"routed experts: {spec.experts} experts in {spec.groups} groups of which {spec.keep_groups} stay open "
+                             f"cannot give {spec.top} choices")
         self.spec, self.rt = spec, rt
+        self.gated = spec.activation == "gated"
         n = spec.names
         # [experts, 2 F, hidden] and [experts, hidden, F]. An expert's gate rows stand before its up rows; where the
         # tcgen05 product runs (bfloat16, widths that are multiples of 8) they stand in blocks of 8 gate rows and the 8
@@ -120,6 +135,8 @@ class RoutedExperts(FeedForward):
                              and os.environ.get("XS_EXPERTS_GEMM", "tcgen05") == "tcgen05")
 
         def stacked(e):
+            if not self.gated:
+                return weights[n["up"].format(e=e)].to(torch.float32)
             g, u = weights[n["gate"].format(e=e)].to(torch.float32), weights[n["up"].format(e=e)].to(torch.float32)
             if self.tensor_cores:
                 return torch.stack([g.view(F // 8, 8, H), u.view(F // 8, 8, H)], 1).reshape(2 * F, H)
@@ -134,6 +151,7 @@ class RoutedExperts(FeedForward):
             router = torch.cat([router, weights[n["shared_gate"]].to(torch.float32).reshape(1, H)], 0)
             self.shared = ClampedGLU(spec.shared, weights, rt)
         self.w_router = rt.matrix(router)
+        self.correction = rt.vector(weights[n["correction"]]) if spec.correction else None
         self.clamp = (spec.limit, spec.alpha, spec.up_shift) if spec.limit > 0 else None
 
     def forward(self, y, step) -> torch.Tensor:
@@ -149,7 +167,11 @@ class RoutedExperts(FeedForward):
         place = ws.get("moe_place", (n,), torch.int32)
         source = ws.get("moe_source", (n,), torch.int32)
         meta = ws.get("moe_meta", (4 + 3 * ops.moe_max_tiles(n, s.experts),), torch.int32)
-        ops.moe_route(logits, s.top, ids, wts, experts=s.experts, scale=s.route_scale)
+        if s.score == "sigmoid":
+            ops.moe_route_grouped(logits, s.top, ids, wts, experts=s.experts, correction=self.correction, groups=s.groups,
+                                  keep=s.keep_groups, group_top=s.group_top, scale=s.route_scale, renorm=s.renorm)
+        else:
+            ops.moe_route(logits, s.top, ids, wts, experts=s.experts, scale=s.route_scale)
         out = ws.get("ffn_out", (T, s.hidden), rt.act_dtype)
         if self.tensor_cores:
             # every expert's rows padded to tiles of 128: gather, two tcgen05 products over the plan's tiles, combine
@@ -160,14 +182,17 @@ class RoutedExperts(FeedForward):
             rows_in = ws.get("moe_rows_in", (128 * tiles, s.hidden), rt.act_dtype)
             ops.moe_gather(y, source, s.top, rows_in)
             act = ws.get("moe_act", (128 * tiles, s.intermediate), rt.act_dtype)
-            ops.gemm_tc_grouped(rows_in, self.w_gate_up, act, meta, tiles, glu=True, clamp=self.clamp)
+            ops.gemm_tc_grouped(rows_in, self.w_gate_up, act, meta, tiles, glu=self.gated, clamp=self.clamp,
+                                relu_squared=not self.gated)
             rows_out = ws.get("moe_rows", (128 * tiles, s.hidden), rt.act_dtype)
             ops.gemm_tc_grouped(act, self.w_down, rows_out, meta, tiles, glu=False)
             ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate)
             return out
         ops.moe_plan(ids, s.experts, place, source, meta)
         act = ws.get("moe_act", (n, s.intermediate), rt.act_dtype)
-        ops.moe_gemm(y, self.w_gate_up, act, meta, n, source, s.top, glu=True, clamp=self.clamp)
+        ops.moe_gemm(y, self.w_gate_up, act, meta, n, source, s.top, glu=self.gated, clamp=self.clamp)
+        if not self.gated:
+            ops.relu_squared(act, act)
         rows_out = ws.get("moe_rows", (n, s.hidden), rt.act_dtype)
         ops.moe_gemm(act, self.w_down, rows_out, meta, n, None, s.top, glu=False)
         ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate)

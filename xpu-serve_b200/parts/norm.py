@@ -1,4 +1,4 @@
-"""RMSNorm over the last dimension, x * (mean(x^2) + eps)^(-1/2) * w, no +1 offset, in float32
+"""RMSNorm over the last dimension, x * (mean(x^2) + eps)^(-1/2) * w (`NormSpec.offset` c: times c + w), in float32
 (src/graph/graph.h:57, src/backend/cpu_ref/ops.cpp:260-281). One kernel adds a pending branch to
 the stream (through the branch's own RMSNorm when the layer is a sandwich), writes the sum back
 and produces the normed rows; in decode steps the few-row products carry this norm across
@@ -20,7 +20,9 @@ class RMSNorm(Norm):
 
     def __init__(self, spec, weights, weight_name: str, rt):
         super().__init__(spec, weights, weight_name, rt)
-        self.w = rt.vector(weights[weight_name])
+        # (a weight stored around zero: the norm multiplies by offset + w, formed once in float32)
+        offset = float(getattr(spec, "offset", 0.0))
+        self.w = rt.vector(weights[weight_name].to(torch.float32) + offset if offset else weights[weight_name])
         self.eps = float(spec.eps)
 
     def normed(self, x: torch.Tensor) -> torch.Tensor:
