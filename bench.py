@@ -161,20 +161,57 @@ def nimelorn_stack_configs(name: str, width: int = 2048, vocab: int = 32768):
 
 
 def run_nimelorn_stacks(batch: int, steps: int, warmup: int, only=None) -> int:
+    return run_stacks("nimelorn", NIMELORN_STACKS, nimelorn_stack_configs, batch, steps, warmup, only)
+
+
+# Tozarax layer stacks (`--workload tozarax`; random weights): every layer holds windowed attention without rotation AND the
+# gated delta-rule memory side by side, so the stack beside it is Nimelorn with one layer of each (attention with wide values
+# under a mask of the same length, then the mLSTM memory of the same head sizes), both with the same routed experts.
+def _delta(heads, kv_heads, dim, vdim, conv=4):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
+
+
+_T_MOE = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+TOZARAX_STACKS = {
+    "parallel_experts": ([(_blocked(16, 4, 64, 128, 1024), _delta(16, 16, 64, 128), _T_MOE)] * 2,
+                         [("attention", _blocked(16, 4, 64, 128, 1024), _N_MOE), ("mlstm", {"heads": 16, "dim": 64, "vdim": 128, "gate_cap": 15.0}, _N_MOE)]),
+    "shared_keys_no_experts": ([(_blocked(32, 8, 64, 64, 1024), _delta(32, 16, 128, 128), None)] * 2,
+                               [("attention", _blocked(32, 8, 64, 64, 1024), {"kind": "dense", "ff": 8192}),
+                                ("mlstm", {"heads": 32, "dim": 128, "vdim": 128, "gate_cap": 15.0}, {"kind": "dense", "ff": 8192})]),
+}
+
+
+def tozarax_stack_configs(name: str, width: int = 2048, vocab: int = 32768):
+    from xpu_serve_b200.config import NimelornConfig, TozaraxConfig
+    layers, beside = TOZARAX_STACKS[name]
+    ours = {"architecture": "Tozarax", "width": width, "vocab": vocab, "max_positions": CONTEXT, "norm": {"eps": 1e-5},
+            "canon": {"taps": 4},
+            "layers": [{"type": "parallel", "mixer": {"left": l, "right": r}, "mlp": f} for l, r, f in layers]}
+    other = {"architecture": "Nimelorn", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
+             "embedding": {"scale": float(width) ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 31}},
+             "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in beside]}
+    return TozaraxConfig.from_json(ours), ("nimelorn", NimelornConfig.from_json(other))
+
+
+def run_tozarax_stacks(batch: int, steps: int, warmup: int, only=None) -> int:
+    return run_stacks("tozarax", TOZARAX_STACKS, tozarax_stack_configs, batch, steps, warmup, only)
+
+
+def run_stacks(workload: str, stacks, configs_of, batch: int, steps: int, warmup: int, only=None) -> int:
     """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 after 2,048-token prompts, CUDA graph) of
-    each Nimelorn stack and of the stack beside it, device-timed as the headline's points are. With XS_PROFILE=1 the
-    kernels' own times are printed after each model (ops.profile_report)."""
+    each stack of the workload and of the stack beside it, device-timed as the headline's points are. With XS_PROFILE=1
+    the kernels' own times are printed after each model (ops.profile_report)."""
     import torch
     from xpu_serve_b200 import load_model
     from xpu_serve_b200.ops import lib as ops
     from xpu_serve_b200.weights import write_random_model
     points = {}
-    for name in NIMELORN_STACKS:
+    for name in stacks:
         if only and name not in only:
             continue
-        ours, (beside_label, beside) = nimelorn_stack_configs(name)
+        ours, (beside_label, beside) = configs_of(name)
         points[name] = {}
-        for label, config in (("nimelorn", ours), (beside_label, beside)):
+        for label, config in ((workload, ours), (beside_label, beside)):
             with tempfile.TemporaryDirectory() as root:
                 folder = write_random_model(os.path.join(root, label), config, seed=0, dtype="bfloat16", std=0.02)
                 model = load_model(folder, dtype="bfloat16")
@@ -193,7 +230,7 @@ def run_nimelorn_stacks(batch: int, steps: int, warmup: int, only=None) -> int:
                                    "parameters_m": round(sum(int(np_prod(ts.shape)) for ts in expected(config).values()) / 1e6, 1)}
             del model
             torch.cuda.empty_cache()
-    print(json.dumps({"workload": "nimelorn", "metric": "prefill tok/s (2,048 tokens) and decode tok/s (batch %d) of two-layer stacks" % batch,
+    print(json.dumps({"workload": workload, "metric": "prefill tok/s (2,048 tokens) and decode tok/s (batch %d) of two-layer stacks" % batch,
                       "dtype": "bf16", "data": "synthetic token ids, random weights N(0, 0.02)", "steps": steps, "warmup": warmup,
                       "width": 2048, "vocab": 32768, "points": points}))
     return 0
@@ -526,8 +563,8 @@ def main() -> int:
                          "at long context), which the default run adds to `points`")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sample"],
                     help="time one part only and print a short line (for profiler captures)")
-    ap.add_argument("--stacks", default=None, help="with --workload saralix or nimelorn: a comma list of the stacks to run (all)")
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["saralix", "nimelorn"],
+    ap.add_argument("--stacks", default=None, help="with --workload saralix, nimelorn or tozarax: a comma list of the stacks to run (all)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["saralix", "nimelorn", "tozarax"],
                     help="instead of the default run: a batch of unequal prompts at another shape of the family")
     args = ap.parse_args()
 
@@ -545,6 +582,8 @@ def main() -> int:
         return run_saralix_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
     if args.workload == "nimelorn":
         return run_nimelorn_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
+    if args.workload == "tozarax":
+        return run_tozarax_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
     if args.workload is not None:
         return run_workload(args.workload, args.layers, args.batch, args.steps)
     args.batch = args.batch or 8

@@ -164,9 +164,30 @@ def route(z: np.ndarray, correction: np.ndarray, top: int, groups: int, keep: in
     return ids, np.take_along_axis(s, ids, 1)
 
 
-def routed_units(f: dict, w: Dict[str, np.ndarray], p: str, x: np.ndarray, logits: Optional[np.ndarray] = None) -> np.ndarray:
+def route_margin(z: np.ndarray, correction: np.ndarray, top: int, groups: int, keep: int) -> np.ndarray:
+    """[T]: by how much each token's choice is decided: the smaller of the gap between the last kept and the first dropped
+    group's score and the gap between the last chosen and the first unchosen open unit's choice score."""
+    T, E = z.shape
+    c = sigmoid(z) + correction
+    per = E // groups
+    out = np.full(T, np.inf)
+    for t in range(T):
+        gs = np.array([np.sort(c[t, g * per:(g + 1) * per])[::-1][:2].sum() for g in range(groups)])
+        order = sorted(range(groups), key=lambda g: (-gs[g], g))
+        if keep < groups:
+            out[t] = gs[order[keep - 1]] - gs[order[keep]]
+        open_ = np.sort(np.concatenate([c[t, g * per:(g + 1) * per] for g in order[:keep]]))[::-1]
+        if top < len(open_):
+            out[t] = min(out[t], open_[top - 1] - open_[top])
+    return out
+
+
+def routed_units(f: dict, w: Dict[str, np.ndarray], p: str, x: np.ndarray, logits: Optional[np.ndarray] = None,
+                 margins: Optional[list] = None) -> np.ndarray:
     r = f["router"]
     z = x @ w[p + "router"].T if logits is None else logits
+    if margins is not None:
+        margins.append(route_margin(z, w[p + "correction"], int(r["top"]), int(r["groups"]["count"]), int(r["groups"]["keep"])))
     ids, wt = route(z, w[p + "correction"], int(r["top"]), int(r["groups"]["count"]), int(r["groups"]["keep"]))
     y = np.zeros((x.shape[0], w[p + "e0.down"].shape[0]))
     for t in range(x.shape[0]):
@@ -178,9 +199,10 @@ def routed_units(f: dict, w: Dict[str, np.ndarray], p: str, x: np.ndarray, logit
 
 # ---------------------------------------------------------------------------------- model
 def forward(cfg: dict, w: Dict[str, np.ndarray], tokens: Sequence[int], streams: Optional[list] = None,
-            router_logits: Optional[dict] = None) -> np.ndarray:
+            router_logits: Optional[dict] = None, margins: Optional[list] = None) -> np.ndarray:
     """Logits [T, vocab] of one sequence from its first token. `streams` (a list) takes what each layer hands on.
-    `router_logits[i]`: layer i's router logits given from outside (a precision test feeds the product path's)."""
+    `router_logits[i]`: layer i's router logits given from outside. `margins` (a list) takes, per routed layer, by how
+    much each token's choice of units is decided (route_margin)."""
     eps = float(cfg["norm"]["eps"])
     s = embedding(w, tokens)
     history = [s]
@@ -194,7 +216,7 @@ def forward(cfg: dict, w: Dict[str, np.ndarray], tokens: Sequence[int], streams:
         if layer.get("mlp") is not None:
             f = unit_rms(s, eps) * (1.0 + w[p + "norm2"])
             z = None if router_logits is None else router_logits.get(i)
-            branch = routed_units(layer["mlp"], w, p + "mlp.", sublayer_input(f, w[p + "canon2"]), z)
+            branch = routed_units(layer["mlp"], w, p + "mlp.", sublayer_input(f, w[p + "canon2"]), z, margins)
             s = s + output_gate(f, w[p + "rg2"], w[p + "rg2.b"]) * branch
         history.append(s)
         s = depth_average(history, w[p + "dwa"])
@@ -202,3 +224,10 @@ def forward(cfg: dict, w: Dict[str, np.ndarray], tokens: Sequence[int], streams:
             streams.append(s)
     y = unit_rms(s, eps) * (1.0 + w["final.norm"])
     return y @ w["head"].T
+
+
+def router_margins(cfg: dict, w: Dict[str, np.ndarray], tokens: Sequence[int]) -> np.ndarray:
+    """[T]: the smallest route_margin over the model's routed layers (infinite without any)."""
+    margins: list = []
+    forward(cfg, w, tokens, margins=margins)
+    return np.min(np.stack(margins), 0) if margins else np.full(len(tokens), np.inf)
