@@ -10,17 +10,21 @@
 // the memory and every sum are float32 in both precision modes.
 //
 // A CTA walks one (sequence, head, tile of value columns) in order. A column's D rows of S live in the registers of PARTS
-// neighbouring lanes (ROWS rows each), so the two sums over a column that a token needs (with kn and with qn) are one pass over
-// the registers and a shuffle; written with u folded in, a token costs that pass and one more:
+// lanes of one warp (ROWS rows each), so the two sums over a column that a token needs (with kn and with qn) are one pass over
+// the registers and a few shuffles; written with u folded in, a token costs that pass and one more:
 //   r = S^T kn, s = S^T qn (old S);  u = beta (v - g r);  o = g s + u (kn . qn);  S <- g S + kn u^T
-// Tokens are staged eight at a time in shared memory (normed keys and queries, kn . qn, g, beta, the tile's values).
+// The recurrence is a chain of dependent operations per entry of S, so a token's time is latency, not arithmetic. The warps
+// that hold S (consumers) therefore do nothing else: kProducers further warps stage the next tokens (normed keys and
+// queries, kn . qn, g, beta, the tile's values) into the other of two buffers in shared memory while the consumers walk
+// the current one, and the two sides meet at one barrier a buffer.
 #include <math.h>
 
 #include "common.cuh"
 
 namespace {
 
-constexpr int kStage = 8;      // tokens staged at a time
+constexpr int kProducers = 4;  // warps that stage tokens
+constexpr int kBatch = 4;      // tokens whose loads a producer warp has in flight together
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
@@ -40,28 +44,107 @@ struct GdArgs {
     float q_scale, unit_eps;
 };
 
+// tokens a buffer: the longer, the better a producer's load latencies are spread; bounded by shared memory
+template <int DP>
+constexpr int stage_tokens() { return DP <= 64 ? 32 : DP <= 128 ? 16 : 8; }
+
 template <typename T, int ROWS, int PARTS>
-__global__ void __launch_bounds__(128) gated_delta_kernel(GdArgs a) {
+__global__ void __launch_bounds__(128 + 32 * kProducers, 2) gated_delta_kernel(GdArgs a) {
     extern __shared__ __align__(16) float smem[];
+    constexpr int DP = ROWS * PARTS;               // rows of S as the registers hold them (>= D; the surplus stays zero)
+    constexpr int STAGE = stage_tokens<DP>();
+    constexpr int NR = (DP + 31) / 32;             // entries of a key a producer lane keeps
     const int D = a.D, Pn = a.P;
-    const int DP = ROWS * PARTS;                   // rows of S as the registers hold them (>= D; the surplus stays zero)
-    const int cols = blockDim.x / PARTS;           // value columns of this CTA
-    float* qs = smem;                              // [kStage][DP]
-    float* ks = qs + kStage * DP;                  // [kStage][DP]
-    float* vs = ks + kStage * DP;                  // [kStage][cols]
-    float* sc = vs + kStage * cols;                // [kStage][4]: g, beta, kn . qn
+    const int consumers = (int)blockDim.x - 32 * kProducers;
+    const int cols = consumers / PARTS;            // value columns of this CTA
+    float* qs = smem;                              // [2][STAGE][DP]
+    float* ks = qs + 2 * STAGE * DP;               // [2][STAGE][DP]
+    float* vs = ks + 2 * STAGE * DP;               // [2][STAGE][cols]
+    float* sc = vs + 2 * STAGE * cols;             // [2][STAGE][4]: g, beta, kn . qn
     pdl_launch_dependents();
     const int h = blockIdx.y, seq = blockIdx.z;
     const int kh = h / (a.heads / a.key_heads);
-    const int part = threadIdx.x % PARTS, col_local = threadIdx.x / PARTS;
-    const int col = blockIdx.x * cols + col_local;
-    const bool live = col < Pn;
+    const bool producer = (int)threadIdx.x >= consumers;
+    const int lane = threadIdx.x & 31;
     const int t0 = a.cu_seqlens[seq], t1 = a.cu_seqlens[seq + 1];
     const int64_t slot = a.slots[seq];
-    const float decay_rate = -expf(a.a_log[h]), dt_b = a.dt_bias[h];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     pdl_wait();
     if (t1 <= t0) return;
+    const int stages = (t1 - t0 + STAGE - 1) / STAGE;
+    const T* qkv = (const T*)a.qkv;
+
+    if (producer) {
+        const int pt = (int)threadIdx.x - consumers, pwarp = pt >> 5;
+        const float decay_rate = -expf(a.a_log[h]), dt_b = a.dt_bias[h];
+        for (int s = 0; s <= stages; ++s) {
+            if (s < stages) {
+                const int base = t0 + s * STAGE, n = min(STAGE, t1 - base);
+                float* qb = qs + (s & 1) * STAGE * DP;
+                float* kb = ks + (s & 1) * STAGE * DP;
+                float* vb = vs + (s & 1) * STAGE * cols;
+                float* sb = sc + (s & 1) * STAGE * 4;
+                // a token a thread: its decay and its step size
+                if (pt < n) {
+                    const float* ab = a.ab + (int64_t)(base + pt) * a.ld_ab;
+                    sb[pt * 4 + 0] = expf(decay_rate * softplus_f(ab[h] + dt_b));
+                    sb[pt * 4 + 1] = 1.0f / (1.0f + expf(-ab[a.heads + h]));
+                }
+                // the tile's values
+#pragma unroll 4
+                for (int idx = pt; idx < n * cols; idx += 32 * kProducers) {
+                    const int i = idx / cols, c = idx - i * cols;
+                    const int gc = blockIdx.x * cols + c;
+                    vb[idx] = gc < Pn ? to_f32(qkv[(int64_t)(base + i) * a.ld + a.v_col + h * Pn + gc]) : 0.0f;
+                }
+                // a warp a token, kBatch tokens' loads together: key and query, their norms and their product
+                for (int g0 = pwarp * kBatch; g0 < n; g0 += kProducers * kBatch) {
+                    float qv[kBatch][NR], kv[kBatch][NR];
+#pragma unroll
+                    for (int j = 0; j < kBatch; ++j) {
+                        const T* row = qkv + (int64_t)(base + min(g0 + j, n - 1)) * a.ld;
+#pragma unroll
+                        for (int r = 0; r < NR; ++r) {
+                            const int d = lane + 32 * r;
+                            qv[j][r] = d < D ? to_f32(row[a.q_col + kh * D + d]) : 0.0f;
+                            kv[j][r] = d < D ? to_f32(row[a.k_col + kh * D + d]) : 0.0f;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < kBatch; ++j) {
+                        float qq = 0.0f, kk = 0.0f, qk = 0.0f;
+#pragma unroll
+                        for (int r = 0; r < NR; ++r) {
+                            qq = fmaf(qv[j][r], qv[j][r], qq);
+                            kk = fmaf(kv[j][r], kv[j][r], kk);
+                            qk = fmaf(qv[j][r], kv[j][r], qk);
+                        }
+                        qq = warp_sum(qq);
+                        kk = warp_sum(kk);
+                        qk = warp_sum(qk);
+                        const float qn = a.q_scale / sqrtf(qq + a.unit_eps), kn = 1.0f / sqrtf(kk + a.unit_eps);
+                        const int i = g0 + j;
+                        if (i < n) {
+#pragma unroll
+                            for (int r = 0; r < NR; ++r) {
+                                const int d = lane + 32 * r;
+                                if (d < DP) {
+                                    qb[i * DP + d] = qv[j][r] * qn;
+                                    kb[i * DP + d] = kv[j][r] * kn;
+                                }
+                            }
+                            if (lane == 0) sb[i * 4 + 2] = qk * qn * kn;
+                        }
+                    }
+                }
+            }
+            __syncthreads();                       // buffer s is full; the consumers are done with the one before it
+        }
+        return;
+    }
+
+    const int part = lane % PARTS, col_local = (int)threadIdx.x / PARTS;
+    const int col = blockIdx.x * cols + col_local;
+    const bool live = col < Pn;
     float S[ROWS];
     float* sg = a.state + ((slot * a.heads + h) * D) * (int64_t)Pn;
 #pragma unroll
@@ -69,67 +152,37 @@ __global__ void __launch_bounds__(128) gated_delta_kernel(GdArgs a) {
         const int d = part * ROWS + r;
         S[r] = (live && d < D) ? sg[(int64_t)d * Pn + col] : 0.0f;
     }
-    const T* qkv = (const T*)a.qkv;
-    for (int base = t0; base < t1; base += kStage) {
-        const int n = min(kStage, t1 - base);
-        __syncthreads();                           // the last stage's readers are done
-        // a warp a token: its key and query, their norms and their product
-        for (int i = warp; i < n; i += warps) {
-            const T* row = qkv + (int64_t)(base + i) * a.ld;
-            float qq = 0.0f, kk = 0.0f;
-            for (int d = lane; d < DP; d += 32) {
-                const float qv = d < D ? to_f32(row[a.q_col + kh * D + d]) : 0.0f;
-                const float kv = d < D ? to_f32(row[a.k_col + kh * D + d]) : 0.0f;
-                qs[i * DP + d] = qv;
-                ks[i * DP + d] = kv;
-                qq = fmaf(qv, qv, qq);
-                kk = fmaf(kv, kv, kk);
-            }
-            qq = warp_sum(qq);
-            kk = warp_sum(kk);
-            const float qn = a.q_scale / sqrtf(qq + a.unit_eps), kn = 1.0f / sqrtf(kk + a.unit_eps);
-            float dot = 0.0f;
-            for (int d = lane; d < DP; d += 32) {
-                const float qv = qs[i * DP + d] * qn, kv = ks[i * DP + d] * kn;
-                qs[i * DP + d] = qv;
-                ks[i * DP + d] = kv;
-                dot = fmaf(qv, kv, dot);
-            }
-            dot = warp_sum(dot);
-            if (lane == 0) {
-                const float* ab = a.ab + (int64_t)(base + i) * a.ld_ab;
-                sc[i * 4 + 0] = expf(decay_rate * softplus_f(ab[h] + dt_b));
-                sc[i * 4 + 1] = 1.0f / (1.0f + expf(-ab[a.heads + h]));
-                sc[i * 4 + 2] = dot;
-            }
-        }
-        for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
-            const int i = idx / cols, c = idx - i * cols;
-            const int gc = blockIdx.x * cols + c;
-            vs[i * cols + c] = gc < Pn ? to_f32(qkv[(int64_t)(base + i) * a.ld + a.v_col + h * Pn + gc]) : 0.0f;
-        }
-        __syncthreads();
+    __syncthreads();                               // buffer 0 is full
+    for (int s = 0; s < stages; ++s) {
+        const int base = t0 + s * STAGE, n = min(STAGE, t1 - base);
+        const float* qb = qs + (s & 1) * STAGE * DP + part * ROWS;
+        const float* kb = ks + (s & 1) * STAGE * DP + part * ROWS;
+        const float* vb = vs + (s & 1) * STAGE * cols + col_local;
+        const float* sb = sc + (s & 1) * STAGE * 4;
+        float* yo = a.y + (int64_t)base * (a.heads * Pn) + h * Pn + col;
+#pragma unroll 2
         for (int i = 0; i < n; ++i) {
-            const float4* k4 = reinterpret_cast<const float4*>(ks + i * DP + part * ROWS);
-            const float4* q4 = reinterpret_cast<const float4*>(qs + i * DP + part * ROWS);
-            float r0 = 0.0f, r1 = 0.0f, s0 = 0.0f, s1 = 0.0f;
+            const float4* k4 = reinterpret_cast<const float4*>(kb + i * DP);
+            const float4* q4 = reinterpret_cast<const float4*>(qb + i * DP);
+            float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f, s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
             for (int r = 0; r < ROWS / 4; ++r) {
                 const float4 kv = k4[r], qv = q4[r];
                 r0 = fmaf(S[4 * r], kv.x, r0); r1 = fmaf(S[4 * r + 1], kv.y, r1);
-                r0 = fmaf(S[4 * r + 2], kv.z, r0); r1 = fmaf(S[4 * r + 3], kv.w, r1);
+                r2 = fmaf(S[4 * r + 2], kv.z, r2); r3 = fmaf(S[4 * r + 3], kv.w, r3);
                 s0 = fmaf(S[4 * r], qv.x, s0); s1 = fmaf(S[4 * r + 1], qv.y, s1);
-                s0 = fmaf(S[4 * r + 2], qv.z, s0); s1 = fmaf(S[4 * r + 3], qv.w, s1);
+                s2 = fmaf(S[4 * r + 2], qv.z, s2); s3 = fmaf(S[4 * r + 3], qv.w, s3);
             }
-            float rk = r0 + r1, sq = s0 + s1;
+            float rk = (r0 + r1) + (r2 + r3), sq = (s0 + s1) + (s2 + s3);
 #pragma unroll
             for (int o = 1; o < PARTS; o <<= 1) {
                 rk += __shfl_xor_sync(0xffffffffu, rk, o);
                 sq += __shfl_xor_sync(0xffffffffu, sq, o);
             }
-            const float g = sc[i * 4 + 0], beta = sc[i * 4 + 1], kq = sc[i * 4 + 2];
-            const float u = beta * (vs[i * cols + col_local] - g * rk);
-            if (live && part == 0) a.y[(int64_t)(base + i) * (a.heads * Pn) + h * Pn + col] = fmaf(u, kq, g * sq);
+            const float4 gbk = *reinterpret_cast<const float4*>(sb + i * 4);   // g, beta, kn . qn
+            const float g = gbk.x;
+            const float u = gbk.y * (vb[i * cols] - g * rk);
+            if (live && part == 0) yo[(int64_t)i * (a.heads * Pn)] = fmaf(u, gbk.z, g * sq);
 #pragma unroll
             for (int r = 0; r < ROWS / 4; ++r) {
                 const float4 kv = k4[r];
@@ -139,6 +192,7 @@ __global__ void __launch_bounds__(128) gated_delta_kernel(GdArgs a) {
                 S[4 * r + 3] = fmaf(kv.w, u, g * S[4 * r + 3]);
             }
         }
+        __syncthreads();                           // this buffer may be filled again; the next one is full
     }
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
@@ -149,11 +203,13 @@ __global__ void __launch_bounds__(128) gated_delta_kernel(GdArgs a) {
 
 template <typename T, int ROWS, int PARTS>
 int launch(const GdArgs& a, int n_seqs, cudaStream_t stream) {
-    int threads = ((a.P * PARTS + 31) / 32) * 32;
-    if (threads > 128) threads = 128;
-    const int cols = threads / PARTS;
-    const size_t smem = (size_t)(2 * kStage * ROWS * PARTS + kStage * cols + kStage * 4) * sizeof(float);
-    xs_launch(gated_delta_kernel<T, ROWS, PARTS>, dim3(ceil_div_i(a.P, cols), a.heads, n_seqs), dim3(threads), smem, stream, a);
+    constexpr int DP = ROWS * PARTS, STAGE = stage_tokens<DP>();
+    int consumers = ((a.P * PARTS + 31) / 32) * 32;
+    if (consumers > 128) consumers = 128;
+    const int cols = consumers / PARTS;
+    const size_t smem = (size_t)(4 * STAGE * DP + 2 * STAGE * cols + 2 * STAGE * 4) * sizeof(float);
+    xs_launch(gated_delta_kernel<T, ROWS, PARTS>, dim3(ceil_div_i(a.P, cols), a.heads, n_seqs),
+              dim3(consumers + 32 * kProducers), smem, stream, a);
     return 0;
 }
 
@@ -173,10 +229,10 @@ XS_API int xs_gated_delta_scan(const void* qkv, int64_t ld, int q_col, int k_col
 #define XS_GO(TT)                                                     \
     do {                                                              \
         if (D <= 16) launch<TT, 16, 1>(a, n_seqs, stream);            \
-        else if (D <= 32) launch<TT, 32, 1>(a, n_seqs, stream);       \
-        else if (D <= 64) launch<TT, 32, 2>(a, n_seqs, stream);       \
-        else if (D <= 128) launch<TT, 64, 2>(a, n_seqs, stream);      \
-        else launch<TT, 64, 4>(a, n_seqs, stream);                    \
+        else if (D <= 32) launch<TT, 16, 2>(a, n_seqs, stream);       \
+        else if (D <= 64) launch<TT, 16, 4>(a, n_seqs, stream);       \
+        else if (D <= 128) launch<TT, 16, 8>(a, n_seqs, stream);      \
+        else launch<TT, 16, 16>(a, n_seqs, stream);                   \
     } while (0)
     XS_DISPATCH_DTYPE(dtype, TT, XS_GO(TT));
 #undef XS_GO
