@@ -279,6 +279,48 @@ def test_causal_filter_kernel_alone(taps, act, residual, dtype):
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][0], outs[2][0])     # however the tokens were cut
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("taps,act,residual", [(4, "silu", False), (3, "none", True), (2, "none", False), (1, "none", True), (5, "silu", True)])
+def test_causal_filter_kernel_in_long_steps(taps, act, residual, dtype):
+    """Steps of 256 tokens and more take the kernel that walks several tokens a thread: sequences of 3, 300, 1, 8 and 61 tokens,
+    so that a thread's tokens lie across two or three sequences and some sequences start inside one, from states that are not
+    zero, against the plain filter; and bit for bit against the same tokens in steps too short for that kernel."""
+    from xpu_serve_b200.ops import lib as ops
+    rng = np.random.default_rng(40 + taps)
+    C, q_lens, slots = 48, [3, 300, 1, 8, 61], [2, 5, 0, 1, 3]
+    T = sum(q_lens)
+    x = torch.from_numpy(rng.standard_normal((T, C + 8))).to(dtype)
+    w = torch.from_numpy(rng.uniform(-0.5, 0.5, (C, taps))).float().cuda()
+    st0 = torch.from_numpy(rng.standard_normal((6, max(taps - 1, 1), C))).to(dtype)
+    cu, seq_of = ragged(q_lens)
+    xd, wd = x.double().numpy()[:, :C], w.double().cpu().numpy()
+    want = np.zeros((T, C))
+    for s, n in enumerate(q_lens):
+        hist = st0[slots[s]].double().numpy()[:taps - 1] if taps > 1 else np.zeros((0, C))
+        f = plain.causal_filter(np.concatenate([hist, xd[cu[s]:cu[s + 1]]]), wd)[len(hist):]
+        if act == "silu":
+            f = plain.silu(f)
+        want[cu[s]:cu[s + 1]] = f + (xd[cu[s]:cu[s + 1]] if residual else 0.0)
+    st = st0.clone().cuda()
+    out = torch.zeros(T, C, dtype=dtype, device="cuda")
+    ops.causal_conv(x.cuda(), w, st, dev_i32(seq_of), dev_i32(cu), dev_i32(slots), out, act=act, residual=residual)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert np.abs(out.double().cpu().numpy() - want).max() <= tol * max(1.0, np.abs(want).max())
+    # the same tokens, a sequence a launch in two pieces (fewer than 256 tokens each): the other kernel
+    st2 = st0.clone().cuda()
+    out2 = torch.zeros(T, C, dtype=dtype, device="cuda")
+    for s, n in enumerate(q_lens):
+        for a, b in ((0, n // 2), (n // 2, n)):
+            if b > a:
+                o = torch.zeros(b - a, C, dtype=dtype, device="cuda")
+                ops.causal_conv(x[cu[s] + a:cu[s] + b].cuda(), w, st2, dev_i32([0] * (b - a)), dev_i32([0, b - a]), dev_i32([slots[s]]), o,
+                                act=act, residual=residual)
+                out2[cu[s] + a:cu[s] + b] = o
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2) and torch.equal(st, st2)
+    assert torch.equal(st[4].cpu(), st0[4])
+
+
 def test_frame_kernels_alone():
     """The gated sum, the weighted sum over earlier results, the normed sum of branches, and the table row plus position row."""
     from xpu_serve_b200.ops import lib as ops

@@ -23,6 +23,7 @@
 
 namespace {
 
+constexpr int kRows = 16;      // rows of S whose products with a key are summed in one chain of four accumulators
 constexpr int kProducers = 4;  // warps that stage tokens
 constexpr int kBatch = 4;      // tokens whose loads a producer warp has in flight together
 
@@ -44,15 +45,18 @@ struct GdArgs {
     float q_scale, unit_eps;
 };
 
-// tokens a buffer: the longer, the better a producer's load latencies are spread; bounded by shared memory
-template <int DP>
-constexpr int stage_tokens() { return DP <= 64 ? 32 : DP <= 128 ? 16 : 8; }
+// tokens a buffer: the longer, the better a producer's load latencies are spread; bounded by shared memory (the widest
+// case, checked where the kernel is launched, is under the 48 KB every kernel may have). Brief steps need no long buffer.
+template <int DP, int JOIN>
+constexpr int stage_tokens() { return JOIN > 1 ? 8 : DP <= 64 ? 32 : DP <= 128 ? 16 : 8; }
 
-template <typename T, int ROWS, int PARTS>
+template <typename T, int BLOCKS, int JOIN>
 __global__ void __launch_bounds__(128 + 32 * kProducers, 2) gated_delta_kernel(GdArgs a) {
     extern __shared__ __align__(16) float smem[];
-    constexpr int DP = ROWS * PARTS;               // rows of S as the registers hold them (>= D; the surplus stays zero)
-    constexpr int STAGE = stage_tokens<DP>();
+    constexpr int ROWS = kRows * JOIN;             // rows of S a lane keeps
+    constexpr int PARTS = BLOCKS / JOIN;           // lanes a column
+    constexpr int DP = kRows * BLOCKS;             // rows of S as the registers hold them (>= D; the surplus stays zero)
+    constexpr int STAGE = stage_tokens<DP, JOIN>();
     constexpr int NR = (DP + 31) / 32;             // entries of a key a producer lane keeps
     const int D = a.D, Pn = a.P;
     const int consumers = (int)blockDim.x - 32 * kProducers;
@@ -160,20 +164,36 @@ __global__ void __launch_bounds__(128 + 32 * kProducers, 2) gated_delta_kernel(G
         const float* vb = vs + (s & 1) * STAGE * cols + col_local;
         const float* sb = sc + (s & 1) * STAGE * 4;
         float* yo = a.y + (int64_t)base * (a.heads * Pn) + h * Pn + col;
-#pragma unroll 2
+#pragma unroll(JOIN == 1 ? 2 : 1)
         for (int i = 0; i < n; ++i) {
             const float4* k4 = reinterpret_cast<const float4*>(kb + i * DP);
             const float4* q4 = reinterpret_cast<const float4*>(qb + i * DP);
-            float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f, s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+            // Blocks of kRows rows are summed each in four chains, and the blocks' sums pairwise, neighbours first: within
+            // the lane for the JOIN blocks it keeps, by shuffles across the lanes of a column. The tree is the same
+            // whatever JOIN is, so every JOIN gives the same bits.
+            float pr[JOIN], ps[JOIN];
 #pragma unroll
-            for (int r = 0; r < ROWS / 4; ++r) {
-                const float4 kv = k4[r], qv = q4[r];
-                r0 = fmaf(S[4 * r], kv.x, r0); r1 = fmaf(S[4 * r + 1], kv.y, r1);
-                r2 = fmaf(S[4 * r + 2], kv.z, r2); r3 = fmaf(S[4 * r + 3], kv.w, r3);
-                s0 = fmaf(S[4 * r], qv.x, s0); s1 = fmaf(S[4 * r + 1], qv.y, s1);
-                s2 = fmaf(S[4 * r + 2], qv.z, s2); s3 = fmaf(S[4 * r + 3], qv.w, s3);
+            for (int j = 0; j < JOIN; ++j) {
+                float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f, s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+                for (int r = j * (kRows / 4); r < (j + 1) * (kRows / 4); ++r) {
+                    const float4 kv = k4[r], qv = q4[r];
+                    r0 = fmaf(S[4 * r], kv.x, r0); r1 = fmaf(S[4 * r + 1], kv.y, r1);
+                    r2 = fmaf(S[4 * r + 2], kv.z, r2); r3 = fmaf(S[4 * r + 3], kv.w, r3);
+                    s0 = fmaf(S[4 * r], qv.x, s0); s1 = fmaf(S[4 * r + 1], qv.y, s1);
+                    s2 = fmaf(S[4 * r + 2], qv.z, s2); s3 = fmaf(S[4 * r + 3], qv.w, s3);
+                }
+                pr[j] = (r0 + r1) + (r2 + r3);
+                ps[j] = (s0 + s1) + (s2 + s3);
             }
-            float rk = (r0 + r1) + (r2 + r3), sq = (s0 + s1) + (s2 + s3);
+#pragma unroll
+            for (int w = 1; w < JOIN; w <<= 1)
+#pragma unroll
+                for (int m = 0; m < JOIN; m += 2 * w) {
+                    pr[m] += pr[m + w];
+                    ps[m] += ps[m + w];
+                }
+            float rk = pr[0], sq = ps[0];
 #pragma unroll
             for (int o = 1; o < PARTS; o <<= 1) {
                 rk += __shfl_xor_sync(0xffffffffu, rk, o);
@@ -201,14 +221,15 @@ __global__ void __launch_bounds__(128 + 32 * kProducers, 2) gated_delta_kernel(G
     }
 }
 
-template <typename T, int ROWS, int PARTS>
+template <typename T, int BLOCKS, int JOIN>
 int launch(const GdArgs& a, int n_seqs, cudaStream_t stream) {
-    constexpr int DP = ROWS * PARTS, STAGE = stage_tokens<DP>();
+    constexpr int DP = kRows * BLOCKS, STAGE = stage_tokens<DP, JOIN>(), PARTS = BLOCKS / JOIN;
     int consumers = ((a.P * PARTS + 31) / 32) * 32;
     if (consumers > 128) consumers = 128;
     const int cols = consumers / PARTS;
     const size_t smem = (size_t)(4 * STAGE * DP + 2 * STAGE * cols + 2 * STAGE * 4) * sizeof(float);
-    xs_launch(gated_delta_kernel<T, ROWS, PARTS>, dim3(ceil_div_i(a.P, cols), a.heads, n_seqs),
+    static_assert((4 * STAGE * DP + 2 * STAGE * (128 / PARTS) + 2 * STAGE * 4) * sizeof(float) <= 48 * 1024, "two buffers of tokens fit");
+    xs_launch(gated_delta_kernel<T, BLOCKS, JOIN>, dim3(ceil_div_i(a.P, cols), a.heads, n_seqs),
               dim3(consumers + 32 * kProducers), smem, stream, a);
     return 0;
 }
@@ -218,7 +239,7 @@ int launch(const GdArgs& a, int n_seqs, cudaStream_t stream) {
 XS_API int xs_gated_delta_scan(const void* qkv, int64_t ld, int q_col, int k_col, int v_col, const float* ab, int64_t ld_ab,
                                const float* a_log, const float* dt_bias, float* state, const int32_t* cu_seqlens,
                                const int32_t* slots, float* y, int n_seqs, int heads, int key_heads, int D, int P, float q_scale,
-                               float unit_eps, int dtype, cudaStream_t stream) {
+                               float unit_eps, int tokens, int dtype, cudaStream_t stream) {
     if (n_seqs == 0) return 0;
     XS_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && heads > 0 && heads <= 65535 && key_heads > 0 && heads % key_heads == 0,
                "gated_delta: %d sequences, %d heads over %d key heads", n_seqs, heads, key_heads);
@@ -226,13 +247,17 @@ XS_API int xs_gated_delta_scan(const void* qkv, int64_t ld, int q_col, int k_col
     XS_REQUIRE(ld_ab >= 2 * heads, "gated_delta: gate rows %lld apart for %d heads", (long long)ld_ab, heads);
     GdArgs a{qkv, ld, q_col, k_col, v_col, ab, ld_ab, a_log, dt_bias, state, cu_seqlens, slots, y, heads, key_heads, D, P,
              q_scale, unit_eps};
-#define XS_GO(TT)                                                     \
-    do {                                                              \
-        if (D <= 16) launch<TT, 16, 1>(a, n_seqs, stream);            \
-        else if (D <= 32) launch<TT, 16, 2>(a, n_seqs, stream);       \
-        else if (D <= 64) launch<TT, 16, 4>(a, n_seqs, stream);       \
-        else if (D <= 128) launch<TT, 16, 8>(a, n_seqs, stream);      \
-        else launch<TT, 16, 16>(a, n_seqs, stream);                   \
+    // A sequence's time is a chain a token long, so long steps spread a column's rows over as many lanes as there are blocks
+    // of kRows rows (short chains, many CTAs). Steps of a token or two a sequence are bound by reading and writing S:
+    // there a lane keeps two blocks, and a CTA twice the columns.
+    const bool brief = tokens <= 2 * n_seqs;
+#define XS_GO(TT)                                                                                    \
+    do {                                                                                             \
+        if (D <= 16) launch<TT, 1, 1>(a, n_seqs, stream);                                            \
+        else if (D <= 32) brief ? launch<TT, 2, 2>(a, n_seqs, stream) : launch<TT, 2, 1>(a, n_seqs, stream);       \
+        else if (D <= 64) brief ? launch<TT, 4, 2>(a, n_seqs, stream) : launch<TT, 4, 1>(a, n_seqs, stream);       \
+        else if (D <= 128) brief ? launch<TT, 8, 2>(a, n_seqs, stream) : launch<TT, 8, 1>(a, n_seqs, stream);      \
+        else brief ? launch<TT, 16, 2>(a, n_seqs, stream) : launch<TT, 16, 1>(a, n_seqs, stream);    \
     } while (0)
     XS_DISPATCH_DTYPE(dtype, TT, XS_GO(TT));
 #undef XS_GO

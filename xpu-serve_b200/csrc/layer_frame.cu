@@ -43,26 +43,130 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t ldx, const f
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int t = blockIdx.x;
     if (c >= C) return;
-    float w[kMaxTaps];
-    for (int k = 0; k < taps; ++k) w[k] = taps_w[(int64_t)c * taps + k];
+    float w[kMaxTaps];                              // by how far back the tap looks (static indices: registers)
+#pragma unroll
+    for (int b = 0; b < kMaxTaps; ++b) w[b] = b < taps ? taps_w[(int64_t)c * taps + (taps - 1 - b)] : 0.0f;
     const int seq = seq_of_token[t];
     const int local = t - cu_seqlens[seq];
     const int64_t slot = slots[seq];
     pdl_wait();
     float acc = 0.0f, cur = 0.0f;
-    for (int k = 0; k < taps; ++k) {
-        const int back = taps - 1 - k;
-        float v;
-        if (local - back >= 0)
-            v = to_f32(x[(int64_t)(t - back) * ldx + c]);
-        else      // state row n - 1 - j holds the input j positions before the step (j = back - local)
-            v = to_f32(state[(slot * (taps - 1) + (taps - 1 - (back - local))) * C + c]);
-        if (back == 0) cur = v;
-        acc = fmaf(w[k], v, acc);
+#pragma unroll
+    for (int back = kMaxTaps - 1; back >= 0; --back) {
+        if (back < taps) {
+            float v;
+            if (local - back >= 0)
+                v = to_f32(x[(int64_t)(t - back) * ldx + c]);
+            else      // state row n - 1 - j holds the input j positions before the step (j = back - local)
+                v = to_f32(state[(slot * (taps - 1) + (taps - 1 - (back - local))) * C + c]);
+            if (back == 0) cur = v;
+            acc = fmaf(w[back], v, acc);
+        }
     }
     if (act == 1) acc = silu_f(acc);
     if (residual) acc += cur;
     out[(int64_t)t * ldo + c] = from_f32<T>(acc);
+}
+
+// 16 bytes of channels at a time, held as floats
+template <typename T>
+struct ConvVec;
+template <>
+struct ConvVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <>
+struct ConvVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint4 r;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+
+constexpr int kTileTaps = 4;     // the tiled kernel's filters have at most this many taps
+constexpr int kTileTokens = 8;   // tokens a thread
+
+// The same sums in the same order as causal_conv_kernel, for long steps: a thread takes 16 bytes of channels and kTileTokens
+// tokens, loads the rows it needs once (all loads in flight together) and keeps them in registers. Only a sequence's first
+// taps - 1 tokens of a step go to its state.
+template <typename T>
+__global__ void __launch_bounds__(128) causal_conv_tile_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ taps_w,
+                                                               const T* __restrict__ state, const int32_t* __restrict__ seq_of_token,
+                                                               const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
+                                                               T* __restrict__ out, int64_t ldo, int C, int taps, int act, int residual,
+                                                               int n_tokens) {
+    constexpr int V = ConvVec<T>::N, ROWS = kTileTokens + kTileTaps - 1;
+    pdl_launch_dependents();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    const int t0 = blockIdx.x * kTileTokens;
+    if (c >= C) return;
+    float w[kTileTaps][V];                          // by how far back the tap looks
+#pragma unroll
+    for (int b = 0; b < kTileTaps; ++b)
+#pragma unroll
+        for (int v = 0; v < V; ++v) w[b][v] = b < taps ? taps_w[(int64_t)(c + v) * taps + (taps - 1 - b)] : 0.0f;
+    pdl_wait();
+    float rows[ROWS][V];                            // row r is token t0 - (kTileTaps - 1) + r
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const int t = t0 - (kTileTaps - 1) + r;
+        if (t >= 0 && t < n_tokens && (r >= kTileTaps - 1 || kTileTaps - 1 - r < taps))
+            ConvVec<T>::load(x + (int64_t)t * ldx + c, rows[r]);
+        else {
+#pragma unroll
+            for (int v = 0; v < V; ++v) rows[r][v] = 0.0f;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kTileTokens; ++i) {
+        const int t = t0 + i;
+        if (t >= n_tokens) break;
+        const int seq = seq_of_token[t];
+        const int local = t - cu_seqlens[seq];
+        float acc[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = 0.0f;
+#pragma unroll
+        for (int back = kTileTaps - 1; back >= 0; --back) {
+            if (back < taps) {
+                if (local - back >= 0) {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[back][v], rows[i + kTileTaps - 1 - back][v], acc[v]);
+                } else {
+                    float sv[V];
+                    ConvVec<T>::load(state + ((int64_t)slots[seq] * (taps - 1) + (taps - 1 - (back - local))) * C + c, sv);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[back][v], sv[v], acc[v]);
+                }
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            if (act == 1) acc[v] = silu_f(acc[v]);
+            if (residual) acc[v] += rows[i + kTileTaps - 1][v];
+        }
+        ConvVec<T>::store(out + (int64_t)t * ldo + c, acc);
+    }
 }
 
 // After the convolution: a sequence's state becomes its last n - 1 inputs (the step's, and the old state's where the step
@@ -170,9 +274,19 @@ XS_API int xs_causal_conv(const void* x, int64_t ldx, const float* taps_w, void*
     XS_REQUIRE(T > 0 && n_seqs > 0 && C <= 65535 * 128 && (act == 0 || act == 1), "causal_conv: %d tokens in %d sequences, %d channels",
                T, n_seqs, C);
     const int tiles = ceil_div_i(C, 128);
-    XS_DISPATCH_DTYPE(dtype, TT,
-                      xs_launch(causal_conv_kernel<TT>, dim3(T, tiles), dim3(128), 0, stream, (const TT*)x, ldx, taps_w,
-                                (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, ldo, C, taps, act, residual));
+    const int vec = dtype == XS_F32 ? 4 : 8;           // channels in 16 bytes
+    const bool aligned = C % vec == 0 && ldx % vec == 0 && ldo % vec == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                         (uintptr_t)state % 16 == 0;
+    if (aligned && taps <= kTileTaps && T >= 256) {
+        XS_DISPATCH_DTYPE(dtype, TT,
+                          xs_launch(causal_conv_tile_kernel<TT>, dim3(ceil_div_i(T, kTileTokens), ceil_div_i(C, 128 * vec)), dim3(128), 0,
+                                    stream, (const TT*)x, ldx, taps_w, (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out,
+                                    ldo, C, taps, act, residual, T));
+    } else {
+        XS_DISPATCH_DTYPE(dtype, TT,
+                          xs_launch(causal_conv_kernel<TT>, dim3(T, tiles), dim3(128), 0, stream, (const TT*)x, ldx, taps_w,
+                                    (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, ldo, C, taps, act, residual));
+    }
     XS_LAUNCH_CHECK("causal_conv");
     if (taps > 1) {
         XS_DISPATCH_DTYPE(dtype, TT,

@@ -77,7 +77,7 @@ def _signatures(lib) -> None:
         "xs_gated_add": [P, P, I, P, L, P, I, I, P],
         "xs_depth_average": [P, L, P, I, P, L, P],
         "xs_rmsnorm_accumulate": [P, I, P, P, I, I, F, F, I, P],
-        "xs_gated_delta_scan": [P, L, I, I, I, P, L, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+        "xs_gated_delta_scan": [P, L, I, I, I, P, L, P, P, P, P, P, P, I, I, I, I, I, F, F, I, I, P],
         "xs_moe_route_grouped": [P, I, I, I, I, P, I, I, I, F, I, P, P, P],
         "xs_mamba2_scan": [P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_mamba2_scan_chunked": [P, P, L, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
@@ -1310,4 +1310,4 @@ def gated_delta_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, ab: 
     _check(load().xs_gated_delta_scan(qkv.data_ptr(), qkv.stride(0), int(q_col), int(k_col), int(v_col), ab.data_ptr(),
                                       ab.stride(0), a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(),
                                       cu_seqlens.data_ptr(), slots.data_ptr(), y.data_ptr(), slots.numel(), int(heads),
-                                      int(key_heads), int(dim), int(vdim), float(q_scale), float(unit_eps), _code(qkv), _stream()))
+                                      int(key_heads), int(dim), int(vdim), float(q_scale), float(unit_eps), int(T), _code(qkv), _stream()))
