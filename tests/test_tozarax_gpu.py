@@ -280,7 +280,8 @@ def test_causal_filter_kernel_alone(taps, act, residual, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps,act,residual", [(4, "silu", False), (3, "none", True), (2, "none", False), (1, "none", True), (5, "silu", True)])
+@pytest.mark.parametrize("taps,act,residual", [(4, "silu", False), (3, "none", True), (2, "none", False), (1, "none", True), (5, "silu", True), (8, "none", False),
+                                               (9, "silu", False)])
 def test_causal_filter_kernel_in_long_steps(taps, act, residual, dtype):
     """Steps of 256 tokens and more take the kernel that walks several tokens a thread: sequences of 3, 300, 1, 8 and 61 tokens,
     so that a thread's tokens lie across two or three sequences and some sequences start inside one, from states that are not

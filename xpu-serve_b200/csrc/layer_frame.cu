@@ -32,7 +32,8 @@ __global__ void embed_pos_kernel(const T* __restrict__ table, const T* __restric
     for (int c = threadIdx.x; c < H; c += blockDim.x) h[(int64_t)t * H + c] = to_f32(a[c]) + to_f32(b[c]);
 }
 
-__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+// (the fast exponential and division: a few units in the last place of float32, in front of a rounding to the activation type)
+__device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ taps_w,
@@ -64,11 +65,11 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t ldx, const f
         }
     }
     if (act == 1) acc = silu_f(acc);
-    if (residual) acc += cur;
+    if (residual) acc = __fadd_rn(acc, cur);          // (never fused with the activation's last product: the same bits in both kernels)
     out[(int64_t)t * ldo + c] = from_f32<T>(acc);
 }
 
-// 16 bytes of channels at a time, held as floats
+// four channels at a time, held as floats
 template <typename T>
 struct ConvVec;
 template <>
@@ -84,53 +85,63 @@ struct ConvVec<float> {
 };
 template <>
 struct ConvVec<__nv_bfloat16> {
-    static constexpr int N = 8;
-    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
-        const uint4 r = *reinterpret_cast<const uint4*>(p);
+    static constexpr int N = 4;                    // (eight channels a thread cost the registers of two more CTAs an SM)
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+        const uint2 r = *reinterpret_cast<const uint2*>(p);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
             const float2 f = __bfloat1622float2(h[i]);
             v[2 * i] = f.x; v[2 * i + 1] = f.y;
         }
     }
-    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
-        uint4 r;
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+        uint2 r;
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-        *reinterpret_cast<uint4*>(p) = r;
+        for (int i = 0; i < 2; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint2*>(p) = r;
     }
 };
 
-constexpr int kTileTaps = 4;     // the tiled kernel's filters have at most this many taps
+constexpr int kTileTaps = 8;     // the tiled kernel's filters have at most this many taps
 constexpr int kTileTokens = 8;   // tokens a thread
 
-// The same sums in the same order as causal_conv_kernel, for long steps: a thread takes 16 bytes of channels and kTileTokens
-// tokens, loads the rows it needs once (all loads in flight together) and keeps them in registers. Only a sequence's first
-// taps - 1 tokens of a step go to its state.
-template <typename T>
+// The same sums in the same order as causal_conv_kernel, for long steps: a thread takes four channels and kTileTokens
+// tokens, loads the rows it needs once (all loads in flight together) and keeps them in registers, with its channels' taps
+// (contiguous in memory: 16 bytes a load). Only a sequence's first TAPS - 1 tokens of a step go to its state.
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(128) causal_conv_tile_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ taps_w,
                                                                const T* __restrict__ state, const int32_t* __restrict__ seq_of_token,
                                                                const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
-                                                               T* __restrict__ out, int64_t ldo, int C, int taps, int act, int residual,
+                                                               T* __restrict__ out, int64_t ldo, int C, int act, int residual,
                                                                int n_tokens) {
-    constexpr int V = ConvVec<T>::N, ROWS = kTileTokens + kTileTaps - 1;
+    constexpr int V = ConvVec<T>::N, ROWS = kTileTokens + TAPS - 1;
     pdl_launch_dependents();
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     const int t0 = blockIdx.x * kTileTokens;
     if (c >= C) return;
-    float w[kTileTaps][V];                          // by how far back the tap looks
+    float w[V * TAPS];                              // channel v's tap k at [v * TAPS + k]
+    {
+        const float4* w4 = reinterpret_cast<const float4*>(taps_w + (int64_t)c * TAPS);
 #pragma unroll
-    for (int b = 0; b < kTileTaps; ++b)
+        for (int i = 0; i < V * TAPS / 4; ++i) {
+            const float4 r = w4[i];
+            w[4 * i] = r.x; w[4 * i + 1] = r.y; w[4 * i + 2] = r.z; w[4 * i + 3] = r.w;
+        }
+    }
+    // every token's place in its sequence, all loads together (a chain of two loads a token otherwise)
+    int seq[kTileTokens], local[kTileTokens];
 #pragma unroll
-        for (int v = 0; v < V; ++v) w[b][v] = b < taps ? taps_w[(int64_t)(c + v) * taps + (taps - 1 - b)] : 0.0f;
+    for (int i = 0; i < kTileTokens; ++i) seq[i] = seq_of_token[min(t0 + i, n_tokens - 1)];
+#pragma unroll
+    for (int i = 0; i < kTileTokens; ++i) local[i] = min(t0 + i, n_tokens - 1) - cu_seqlens[seq[i]];
     pdl_wait();
-    float rows[ROWS][V];                            // row r is token t0 - (kTileTaps - 1) + r
+    float rows[ROWS][V];                            // row r is token t0 - (TAPS - 1) + r
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-        const int t = t0 - (kTileTaps - 1) + r;
-        if (t >= 0 && t < n_tokens && (r >= kTileTaps - 1 || kTileTaps - 1 - r < taps))
+        const int t = t0 - (TAPS - 1) + r;
+        if (t >= 0 && t < n_tokens)
             ConvVec<T>::load(x + (int64_t)t * ldx + c, rows[r]);
         else {
 #pragma unroll
@@ -140,32 +151,29 @@ __global__ void __launch_bounds__(128) causal_conv_tile_kernel(const T* __restri
 #pragma unroll
     for (int i = 0; i < kTileTokens; ++i) {
         const int t = t0 + i;
-        if (t >= n_tokens) break;
-        const int seq = seq_of_token[t];
-        const int local = t - cu_seqlens[seq];
-        float acc[V];
+        if (t < n_tokens) {
+            float acc[V];
 #pragma unroll
-        for (int v = 0; v < V; ++v) acc[v] = 0.0f;
+            for (int v = 0; v < V; ++v) acc[v] = 0.0f;
 #pragma unroll
-        for (int back = kTileTaps - 1; back >= 0; --back) {
-            if (back < taps) {
-                if (local - back >= 0) {
+            for (int back = TAPS - 1; back >= 0; --back) {
+                if (local[i] - back >= 0) {
 #pragma unroll
-                    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[back][v], rows[i + kTileTaps - 1 - back][v], acc[v]);
+                    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[v * TAPS + TAPS - 1 - back], rows[i + TAPS - 1 - back][v], acc[v]);
                 } else {
                     float sv[V];
-                    ConvVec<T>::load(state + ((int64_t)slots[seq] * (taps - 1) + (taps - 1 - (back - local))) * C + c, sv);
+                    ConvVec<T>::load(state + ((int64_t)slots[seq[i]] * (TAPS - 1) + (TAPS - 1 - (back - local[i]))) * C + c, sv);
 #pragma unroll
-                    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[back][v], sv[v], acc[v]);
+                    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[v * TAPS + TAPS - 1 - back], sv[v], acc[v]);
                 }
             }
-        }
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-            if (act == 1) acc[v] = silu_f(acc[v]);
-            if (residual) acc[v] += rows[i + kTileTaps - 1][v];
+            for (int v = 0; v < V; ++v) {
+                if (act == 1) acc[v] = silu_f(acc[v]);
+                if (residual) acc[v] = __fadd_rn(acc[v], rows[i + TAPS - 1][v]);
+            }
+            ConvVec<T>::store(out + (int64_t)t * ldo + c, acc);
         }
-        ConvVec<T>::store(out + (int64_t)t * ldo + c, acc);
     }
 }
 
@@ -274,14 +282,24 @@ XS_API int xs_causal_conv(const void* x, int64_t ldx, const float* taps_w, void*
     XS_REQUIRE(T > 0 && n_seqs > 0 && C <= 65535 * 128 && (act == 0 || act == 1), "causal_conv: %d tokens in %d sequences, %d channels",
                T, n_seqs, C);
     const int tiles = ceil_div_i(C, 128);
-    const int vec = dtype == XS_F32 ? 4 : 8;           // channels in 16 bytes
+    const int vec = 4;                             // channels a thread
     const bool aligned = C % vec == 0 && ldx % vec == 0 && ldo % vec == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
-                         (uintptr_t)state % 16 == 0;
+                         (uintptr_t)state % 16 == 0 && (uintptr_t)taps_w % 16 == 0;
     if (aligned && taps <= kTileTaps && T >= 256) {
-        XS_DISPATCH_DTYPE(dtype, TT,
-                          xs_launch(causal_conv_tile_kernel<TT>, dim3(ceil_div_i(T, kTileTokens), ceil_div_i(C, 128 * vec)), dim3(128), 0,
-                                    stream, (const TT*)x, ldx, taps_w, (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out,
-                                    ldo, C, taps, act, residual, T));
+#define XS_TILE(TT, N)                                                                                                         \
+    xs_launch(causal_conv_tile_kernel<TT, N>, dim3(ceil_div_i(T, kTileTokens), ceil_div_i(C, 128 * vec)), dim3(128), 0, stream, \
+              (const TT*)x, ldx, taps_w, (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, ldo, C, act, residual, T)
+        XS_DISPATCH_DTYPE(dtype, TT, do {
+            if (taps == 1) XS_TILE(TT, 1);
+            else if (taps == 2) XS_TILE(TT, 2);
+            else if (taps == 3) XS_TILE(TT, 3);
+            else if (taps == 4) XS_TILE(TT, 4);
+            else if (taps == 5) XS_TILE(TT, 5);
+            else if (taps == 6) XS_TILE(TT, 6);
+            else if (taps == 7) XS_TILE(TT, 7);
+            else XS_TILE(TT, 8);
+        } while (0));
+#undef XS_TILE
     } else {
         XS_DISPATCH_DTYPE(dtype, TT,
                           xs_launch(causal_conv_kernel<TT>, dim3(T, tiles), dim3(128), 0, stream, (const TT*)x, ldx, taps_w,
