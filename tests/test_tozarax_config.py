@@ -38,7 +38,7 @@ def test_every_size_and_constant_comes_from_the_file():
     assert a.position is None and not a.qk_norm and not a.head_gate
     assert (m.kind, m.heads, m.kv_heads, m.dim, m.vdim, m.taps, m.eps) == ("gated_delta", 4, 2, 10, 14, 2, 3e-6)
     b, n = spec.layers[1].mixer.branches
-    assert (b.heads, b.kv_heads, b.head_dim, b.v_dim, b.window, b.scale) == (6, 3, 10, 6, 40, 0.35)
+    assert (b.heads, b.kv_heads, b.head_dim, b.v_dim, b.window, b.scale) == (6, 3, 10, 6, 41, 0.35)
     assert (n.heads, n.kv_heads, n.dim, n.vdim, n.taps) == (3, 1, 6, 9, 5)
     f0, f2 = spec.layers[0].ffn, spec.layers[2].ffn
     assert spec.layers[1].ffn is None

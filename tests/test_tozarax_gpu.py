@@ -250,7 +250,7 @@ def test_causal_filter_kernel_alone(taps, act, residual, dtype):
         want[cu[s]:cu[s + 1]] = f + (xd[cu[s]:cu[s + 1]] if residual else 0.0)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
 
-    def run(cuts):
+    def run(cuts, single=False):
         st = st0.clone().cuda()
         out = torch.zeros(T, C, dtype=dtype, device="cuda")
         done = [0] * len(q_lens)
@@ -261,14 +261,15 @@ def test_causal_filter_kernel_alone(taps, act, residual, dtype):
             xs = x[rows].cuda()
             o = torch.zeros(len(rows), C, dtype=dtype, device="cuda")
             c2, so2 = ragged(take)
-            ops.causal_conv(xs, wd_dev, st, dev_i32(so2), dev_i32(c2), dev_i32([slots[s] for s in live]), o, act=act, residual=residual)
+            ops.causal_conv(xs, wd_dev, st, dev_i32(so2), dev_i32(c2), dev_i32([slots[s] for s in live]), o, act=act, residual=residual,
+                            all_single=single)
             out[rows] = o
             for s, k in zip(live, take):
                 done[s] += k
         return out.double().cpu().numpy(), st.double().cpu().numpy()
 
     wd_dev = w.cuda()
-    outs = [run(10 ** 6), run(1), run(2)]
+    outs = [run(10 ** 6), run(1), run(2), run(1, single=True)]     # (the last: the one kernel that also moves the state)
     for out, st in outs:
         assert np.abs(out - want).max() <= tol * max(1.0, np.abs(want).max())
         for s, n in enumerate(q_lens):
@@ -276,7 +277,7 @@ def test_causal_filter_kernel_alone(taps, act, residual, dtype):
                 full = np.concatenate([st0[slots[s]].double().numpy()[:taps - 1], xd[cu[s]:cu[s + 1]]])
                 assert np.array_equal(st[slots[s]][:taps - 1], full[-(taps - 1):])
         assert np.array_equal(st[2], st0[2].double().numpy())          # a slot that no sequence of the step holds
-    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][0], outs[2][0])     # however the tokens were cut
+    assert all(np.array_equal(outs[0][0], o) for o, _ in outs[1:])     # however the tokens were cut
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -357,7 +358,7 @@ def test_frame_kernels_alone():
     assert np.abs(out.double().cpu().numpy() - (table[ids] + rows[pos])).max() < 1e-6
 
 
-@pytest.mark.parametrize("E,top,groups,keep", [(8, 3, 4, 3), (6, 2, 3, 2), (12, 3, 4, 2), (16, 2, 8, 4), (3, 1, 1, 1), (40, 4, 5, 2),
+@pytest.mark.parametrize("E,top,groups,keep", [(10, 3, 5, 3), (6, 2, 3, 2), (12, 3, 4, 2), (16, 2, 8, 4), (3, 1, 1, 1), (40, 4, 5, 2),
                                                (8, 2, 8, 3), (64, 8, 8, 4)])
 def test_grouped_routing_kernel_alone(E, top, groups, keep):
     """Choices and weights against the plain routing for tokens whose choice is no close call; corrections large enough that

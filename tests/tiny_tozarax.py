@@ -35,7 +35,7 @@ def model(width, vocab, taps, layers, eps=1e-5, positions=512):
 CONFIGS = {
     "A": model(44, 203, 3, [
         (left(4, 2, 12, 20, 13, 0.21), right(4, 2, 10, 14, 2), moe(20, 6, 2, 3, 2)),
-        (left(6, 3, 10, 6, 40, 0.35), right(3, 1, 6, 9, 5), None),
+        (left(6, 3, 10, 6, 41, 0.35), right(3, 1, 6, 9, 5), None),
         (left(2, 1, 18, 18, 29, 0.3), right(2, 2, 20, 5, 4), moe(12, 8, 3, 2, 1)),
     ], eps=3e-6),
     "B": model(128, 384, 1, [

@@ -37,9 +37,9 @@ __device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + _
 
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ taps_w,
-                                   const T* __restrict__ state, const int32_t* __restrict__ seq_of_token,
+                                   T* __restrict__ state, const int32_t* __restrict__ seq_of_token,
                                    const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
-                                   T* __restrict__ out, int64_t ldo, int C, int taps, int act, int residual) {
+                                   T* __restrict__ out, int64_t ldo, int C, int taps, int act, int residual, int move_state) {
     pdl_launch_dependents();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int t = blockIdx.x;
@@ -62,6 +62,9 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t ldx, const f
                 v = to_f32(state[(slot * (taps - 1) + (taps - 1 - (back - local))) * C + c]);
             if (back == 0) cur = v;
             acc = fmaf(w[back], v, acc);
+            // A step of one token a sequence moves the state on here: the input `back` positions before this token is
+            // back + 1 before the next, a row that this thread has read already (it walks from the far end).
+            if (move_state && back < taps - 1) state[(slot * (taps - 1) + (taps - 2 - back)) * C + c] = from_f32<T>(v);
         }
     }
     if (act == 1) acc = silu_f(acc);
@@ -276,8 +279,9 @@ XS_API int xs_embed_pos(const void* table, const void* rows, int dtype, const in
 // of the filter's sum. residual 1: the token's own input is added behind the activation.
 XS_API int xs_causal_conv(const void* x, int64_t ldx, const float* taps_w, void* state, const int32_t* seq_of_token,
                           const int32_t* cu_seqlens, const int32_t* slots, void* out, int64_t ldo, int T, int n_seqs, int C,
-                          int taps, int act, int residual, int dtype, cudaStream_t stream) {
+                          int taps, int act, int residual, int all_single, int dtype, cudaStream_t stream) {
     if (T == 0) return 0;
+    XS_REQUIRE(!all_single || T == n_seqs, "causal_conv: %d tokens for %d sequences of one token each", T, n_seqs);
     XS_REQUIRE(C > 0 && taps >= 1 && taps <= kMaxTaps, "causal_conv: %d channels, %d taps (at most %d)", C, taps, kMaxTaps);
     XS_REQUIRE(T > 0 && n_seqs > 0 && C <= 65535 * 128 && (act == 0 || act == 1), "causal_conv: %d tokens in %d sequences, %d channels",
                T, n_seqs, C);
@@ -285,7 +289,7 @@ XS_API int xs_causal_conv(const void* x, int64_t ldx, const float* taps_w, void*
     const int vec = 4;                             // channels a thread
     const bool aligned = C % vec == 0 && ldx % vec == 0 && ldo % vec == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                          (uintptr_t)state % 16 == 0 && (uintptr_t)taps_w % 16 == 0;
-    if (aligned && taps <= kTileTaps && T >= 256) {
+    if (aligned && taps <= kTileTaps && T >= 256 && !all_single) {
 #define XS_TILE(TT, N)                                                                                                         \
     xs_launch(causal_conv_tile_kernel<TT, N>, dim3(ceil_div_i(T, kTileTokens), ceil_div_i(C, 128 * vec)), dim3(128), 0, stream, \
               (const TT*)x, ldx, taps_w, (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, ldo, C, act, residual, T)
@@ -303,7 +307,12 @@ XS_API int xs_causal_conv(const void* x, int64_t ldx, const float* taps_w, void*
     } else {
         XS_DISPATCH_DTYPE(dtype, TT,
                           xs_launch(causal_conv_kernel<TT>, dim3(T, tiles), dim3(128), 0, stream, (const TT*)x, ldx, taps_w,
-                                    (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, ldo, C, taps, act, residual));
+                                    (TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, ldo, C, taps, act, residual,
+                                    all_single && taps > 1 ? 1 : 0));
+        if (all_single) {
+            XS_LAUNCH_CHECK("causal_conv");
+            return 0;
+        }
     }
     XS_LAUNCH_CHECK("causal_conv");
     if (taps > 1) {

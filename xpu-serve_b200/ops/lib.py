@@ -73,7 +73,7 @@ def _signatures(lib) -> None:
         "xs_latent_attention_mma": [P, L, L, P, P, P, I, P, P, P, L, P, P, L, L, P, L, I, I, I, I, I, I, I, F, I, I, P],
         "xs_mamba2_conv": [P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P],
         "xs_embed_pos": [P, P, I, P, P, P, I, I, P],
-        "xs_causal_conv": [P, L, P, P, P, P, P, P, L, I, I, I, I, I, I, I, P],
+        "xs_causal_conv": [P, L, P, P, P, P, P, P, L, I, I, I, I, I, I, I, I, P],
         "xs_gated_add": [P, P, I, P, L, P, I, I, P],
         "xs_depth_average": [P, L, P, I, P, L, P],
         "xs_rmsnorm_accumulate": [P, I, P, P, I, I, F, F, I, P],
@@ -1238,9 +1238,10 @@ def embed_pos(table: torch.Tensor, rows: torch.Tensor, ids: torch.Tensor, positi
 
 def causal_conv(x: torch.Tensor, taps_w: torch.Tensor, state: torch.Tensor, seq_of_token: torch.Tensor,
                 cu_seqlens: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, act: str = "none",
-                residual: bool = False) -> None:
+                residual: bool = False, all_single: bool = False) -> None:
     """out[t, c] = (x[t, c] with `residual`) + act(sum_j taps_w[c, j] * x[t - (n - 1) + j, c]) within each sequence, the
-    inputs before the step from `state` [*, n - 1, C] (x's element type), which is then moved on. act: "none" | "silu"."""
+    inputs before the step from `state` [*, n - 1, C] (x's element type), which is then moved on. act: "none" | "silu".
+    `all_single`: every sequence brings exactly one token (the one kernel then also moves the state)."""
     if act not in ("none", "silu"):
         raise KernelError(f"causal_conv: activation '{act}' (none, silu)")
     _need(taps_w, "taps", torch.float32); _need(state, "state", x.dtype)
@@ -1253,8 +1254,8 @@ def causal_conv(x: torch.Tensor, taps_w: torch.Tensor, state: torch.Tensor, seq_
         raise KernelError(f"causal_conv: state is {tuple(state.shape)}, expected [*, {taps - 1}, {C}]")
     _check(load().xs_causal_conv(x.data_ptr(), x.stride(0), taps_w.data_ptr(), state.data_ptr(), seq_of_token.data_ptr(),
                                  cu_seqlens.data_ptr(), slots.data_ptr(), out.data_ptr(), out.stride(0), T, slots.numel(), C,
-                                 taps, 1 if act == "silu" else 0, 1 if residual else 0, _code(x), _stream()),
-           kernels=2 if taps > 1 else 1)
+                                 taps, 1 if act == "silu" else 0, 1 if residual else 0, 1 if all_single else 0, _code(x), _stream()),
+           kernels=2 if taps > 1 and not all_single else 1)
 
 
 def gated_add(h: torch.Tensor, branch: torch.Tensor, logits: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:

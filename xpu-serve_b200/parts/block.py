@@ -349,7 +349,7 @@ class GatedPreNormBlock:
         if sub in self.taps:
             x = rt.ws.get("filtered_input", tuple(a.shape), a.dtype)
             state = rows_view.storage if rows_view is not None else a      # (one tap keeps nothing)
-            ops.causal_conv(a, self.taps[sub], state, step.seq_of_token, step.cu_seqlens, step.slots, x, residual=True)
+            ops.causal_conv(a, self.taps[sub], state, step.seq_of_token, step.cu_seqlens, step.slots, x, residual=True, all_single=step.decode)
         branch = run(x)
         if logits is None:
             stream.add(branch)

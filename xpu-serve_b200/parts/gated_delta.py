@@ -84,7 +84,7 @@ class GatedDeltaMixer(Mixer):
         proj = rt.linear(x, self.w_in, "gd_proj")
         ab = rt.linear(x, self.w_ab, "gd_gates", out_dtype=torch.float32)
         qkv = rt.ws.get("gd_qkv", (T, C), rt.act_dtype)
-        ops.causal_conv(proj, self.taps, cache[0].storage, step.seq_of_token, step.cu_seqlens, step.slots, qkv, act="silu")
+        ops.causal_conv(proj, self.taps, cache[0].storage, step.seq_of_token, step.cu_seqlens, step.slots, qkv, act="silu", all_single=step.decode)
         y = rt.ws.get("gd_y", (T, self.vd), torch.float32)
         ops.gated_delta_scan(qkv, 0, self.kd, 2 * self.kd, ab, self.a_log, self.dt_bias, cache[1].storage, step.cu_seqlens,
                              step.slots, y, s.heads, s.kv_heads, s.dim, s.vdim, float(s.dim) ** -0.5, s.unit_eps)
