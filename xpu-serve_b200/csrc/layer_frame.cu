@@ -32,8 +32,13 @@ __global__ void embed_pos_kernel(const T* __restrict__ table, const T* __restric
     for (int c = threadIdx.x; c < H; c += blockDim.x) h[(int64_t)t * H + c] = to_f32(a[c]) + to_f32(b[c]);
 }
 
-// (the fast exponential and division: a few units in the last place of float32, in front of a rounding to the activation type)
-__device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+// SiLU of a filter's sum. In front of a rounding to bfloat16 the fast exponential and division do (a few units in the last
+// place of float32); float32 activations take the exact ones.
+template <typename T>
+__device__ __forceinline__ float silu_f(float v) {
+    if constexpr (sizeof(T) == 4) return v / (1.0f + expf(-v));
+    else return __fdividef(v, 1.0f + __expf(-v));
+}
 
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ taps_w,
@@ -67,7 +72,7 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t ldx, const f
             if (move_state && back < taps - 1) state[(slot * (taps - 1) + (taps - 2 - back)) * C + c] = from_f32<T>(v);
         }
     }
-    if (act == 1) acc = silu_f(acc);
+    if (act == 1) acc = silu_f<T>(acc);
     if (residual) acc = __fadd_rn(acc, cur);          // (never fused with the activation's last product: the same bits in both kernels)
     out[(int64_t)t * ldo + c] = from_f32<T>(acc);
 }
@@ -172,7 +177,7 @@ __global__ void __launch_bounds__(128) causal_conv_tile_kernel(const T* __restri
             }
 #pragma unroll
             for (int v = 0; v < V; ++v) {
-                if (act == 1) acc[v] = silu_f(acc[v]);
+                if (act == 1) acc[v] = silu_f<T>(acc[v]);
                 if (residual) acc[v] = __fadd_rn(acc[v], rows[i + TAPS - 1][v]);
             }
             ConvVec<T>::store(out + (int64_t)t * ldo + c, acc);
