@@ -1,4 +1,4 @@
-"""A B200-native model library (LFM3, Saralix, Nimelorn, Tozarax): from a request's tokens to its next token.
+"""A B200-native model library (LFM3, Saralix, Nimelorn, Tozarax, Vekuzen): from a request's tokens to its next token.
 
 Import as `xpu_serve_b200`. Importing the package needs no GPU; the CUDA extension is
 compiled and loaded when a model is first put on a device.
@@ -6,13 +6,14 @@ compiled and loaded when a model is first put on a device.
 __version__ = "0.1.0"
 
 from . import registry                                   # noqa: E402
-from .config import ConfigError, Lfm3Config, NimelornConfig, SaralixConfig, TozaraxConfig   # noqa: E402
+from .config import ConfigError, Lfm3Config, NimelornConfig, SaralixConfig, TozaraxConfig, VekuzenConfig   # noqa: E402
 from . import parts                                      # noqa: E402,F401  (registers the parts)
 
 registry.register_architecture("lfm3", Lfm3Config, aliases=("lfm3_vl", "Lfm3ForCausalLM"))
 registry.register_architecture("saralix", SaralixConfig, aliases=("Saralix",))
 registry.register_architecture("nimelorn", NimelornConfig, aliases=("Nimelorn",))
 registry.register_architecture("tozarax", TozaraxConfig, aliases=("Tozarax",))
+registry.register_architecture("vekuzen", VekuzenConfig, aliases=("Vekuzen",))
 
 
 def load_model(folder, dtype="bfloat16", device="cuda:0"):

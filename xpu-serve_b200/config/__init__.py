@@ -4,8 +4,9 @@ from .lfm3 import Lfm3Config, Lfm3Rope
 from .saralix import SaralixConfig
 from .nimelorn import NimelornConfig
 from .tozarax import TozaraxConfig
+from .vekuzen import VekuzenConfig
 from .spec import (AttentionSpec, LayerCall, LayerSpec, ModelSpec, NormSpec, RopeSpec,
                    ShortConvSpec, SwiGLUSpec)
 
-__all__ = ["ConfigError", "read_json", "Lfm3Config", "Lfm3Rope", "SaralixConfig", "NimelornConfig", "TozaraxConfig", "AttentionSpec", "LayerCall",
+__all__ = ["ConfigError", "read_json", "Lfm3Config", "Lfm3Rope", "SaralixConfig", "NimelornConfig", "TozaraxConfig", "VekuzenConfig", "AttentionSpec", "LayerCall",
            "LayerSpec", "ModelSpec", "NormSpec", "RopeSpec", "ShortConvSpec", "SwiGLUSpec"]

@@ -76,13 +76,15 @@ class ShortConvSpec:
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
-    """down(silu(gate x) * up x) (src/models/common/blocks.cpp:23-27)."""
+    """down(act(gate x) * up x) (src/models/common/blocks.cpp:23-27). `activation` "silu" (SwiGLU, LFM3's) or "gelu_tanh":
+    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))."""
     hidden: int
     intermediate: int
     names: Dict[str, str] = field(default_factory=lambda: {
         "gate": "feed_forward.w1.weight", "up": "feed_forward.w3.weight",
         "down": "feed_forward.w2.weight"})
     kind: str = "swiglu"
+    activation: str = "silu"
 
 
 @dataclass(frozen=True)
@@ -117,7 +119,10 @@ class LatentAttentionSpec:
     (`kv_rank` numbers, unit RMS times a weight) and of one rotated key part (`rot_dim` numbers) that the heads
     share. A query head has `dim` unrotated and `rot_dim` rotated channels; a value head `vdim`.
     window 0: every earlier key; W > 0: keys with pos - j < W. `sink`: a learned number per head joins the softmax's
-    denominator. `head_gate`: o[t, h, :] *= sigmoid((x Wg^T)[t, h])."""
+    denominator. `head_gate`: o[t, h, :] *= sigmoid((x Wg^T)[t, h]). `out_gate`: every channel of the concatenated heads is
+    multiplied by sigmoid((x Wg^T)[t, c]) instead (names["gate"] then has heads * vdim rows). `q_rank` > 0: the queries come
+    through a latent of their own, q = Wuq (unit_rms(Wdq x) * w) (names "q_down", "q_norm", "q_up"; the latent norm's eps).
+    rot_dim may be 0 (no rotated part; `position` None)."""
     hidden: int
     heads: int
     dim: int
@@ -132,8 +137,28 @@ class LatentAttentionSpec:
     head_gate: bool = False
     names: Dict[str, str] = field(default_factory=lambda: {
         "q": "mix.q", "down": "mix.dkv", "latent_norm": "mix.dkv.norm", "up_k": "mix.uk", "up_v": "mix.uv",
-        "gate": "mix.g", "sink": "mix.sink", "o": "mix.o"})
+        "gate": "mix.g", "sink": "mix.sink", "o": "mix.o",
+        "q_down": "mix.dq", "q_norm": "mix.dq.norm", "q_up": "mix.uq"})
     kind: str = "latent_attention"
+    out_gate: bool = False
+    q_rank: int = 0
+
+
+@dataclass(frozen=True)
+class LightningSpec:
+    """A linear-attention memory per head with a constant decay: S <- decay_h S + k v^T (S [dim, vdim], float32, zero at a
+    sequence's start), o = S^T q with the new S, for q = silu(Wq x), k = silu(Wk x) (heads of `dim`) and v = silu(Wv x)
+    (heads of `vdim`), no other scale. The concatenated heads are divided by their root mean square over all of them
+    (`eps`), multiplied by a weight and by sigmoid(Wg x), then projected."""
+    hidden: int
+    heads: int
+    dim: int
+    vdim: int
+    decay: Tuple[float, ...]
+    eps: float
+    names: Dict[str, str] = field(default_factory=lambda: {
+        "q": "mix.q", "k": "mix.k", "v": "mix.v", "gate": "mix.g", "o": "mix.o", "norm": "mix.norm"})
+    kind: str = "lightning"
 
 
 @dataclass(frozen=True)
@@ -215,7 +240,12 @@ class RoutedExpertsSpec:
     a learned number per expert (`correction`, names["correction"]; the weights are the scores without it), among the
     `keep_groups` of `groups` equal groups of neighbouring experts whose `group_top` largest such sums add up highest
     (experts of the other groups cannot be chosen); the weights are the chosen scores times `route_scale`, divided by their
-    sum only with `renorm`. `activation` "relu_squared": an expert is down(max(up x, 0)^2), without a gate matrix."""
+    sum only with `renorm`. `activation` "relu_squared": an expert is down(max(up x, 0)^2), without a gate matrix.
+
+    `score` "softmax_all": a token's scores are the softmax over all router outputs; the experts are chosen by score plus
+    `correction` (when set) and weighted by their scores times `route_scale`, as they are. `identity` n > 0: the router has n
+    more outputs behind the experts'; such a choice stands for the token's input itself (times its weight) and has no
+    tensors. `shared` may be any gated unit's spec (ClampedGLUSpec, or SwiGLUSpec for a plain gated unit)."""
     hidden: int
     intermediate: int
     experts: int
@@ -224,12 +254,13 @@ class RoutedExpertsSpec:
     limit: float = 0.0
     alpha: float = 1.702
     up_shift: float = 1.0
-    shared: Optional["ClampedGLUSpec"] = None
+    shared: Optional[object] = None
     names: Dict[str, str] = field(default_factory=lambda: {
         "router": "mlp.router", "gate": "mlp.e{e}.gate", "up": "mlp.e{e}.up", "down": "mlp.e{e}.down",
         "shared_gate": "mlp.shared.sg", "correction": "mlp.correction"})
     kind: str = "routed_experts"
-    score: str = "softmax"           # "softmax" over the chosen logits | "sigmoid" of each logit
+    score: str = "softmax"           # "softmax" over the chosen logits | "sigmoid" of each logit | "softmax_all"
+    identity: int = 0                # router outputs behind the experts' that stand for the token's input itself
     correction: bool = False         # sigmoid scores: a learned number per expert joins the score for the choice only
     groups: int = 1
     keep_groups: int = 1
@@ -276,12 +307,13 @@ class ParallelMixerSpec:
 
 @dataclass(frozen=True)
 class LearnedPositionEmbeddingSpec:
-    """Token embedding = table[tok] + rows[position]: a learned vector per position, `positions` of them."""
+    """Token embedding = table[tok] * scale + rows[position]: a learned vector per position, `positions` of them."""
     width: int
     vocab: int
     positions: int
     names: Dict[str, str] = field(default_factory=lambda: {"table": "embed", "rows": "pos"})
     kind: str = "learned_position"
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -312,6 +344,21 @@ class PairHashEmbeddingSpec:
 
 
 @dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer input from the token itself, behind the layer's last sublayer: with e = table[tok, offset : offset + dim]
+    (a second token table that all layers share, `table` its name at the model's top level, `columns` wide),
+    h += unit_rms(P (gelu_tanh(G h) * e)) * w, the norm's weight plain (names "gate": [dim, width], "proj": [width, dim],
+    "norm": [width], under the layer's prefix)."""
+    dim: int
+    offset: int
+    columns: int
+    vocab: int
+    eps: float
+    table: str = "side.embed"
+    names: Dict[str, str] = field(default_factory=lambda: {"gate": "side.gate", "proj": "side.proj", "norm": "side.norm"})
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One decoder layer: h += post(mixer(pre(h))); h += post(ffn(pre(h)))
     (src/models/lfm3/lfm3_decoder.cpp:78-90). With `sandwich` false the post norms are
@@ -334,6 +381,7 @@ class LayerSpec:
                              # "mixer_gate_bias", "ffn_gate", "ffn_gate_bias"), x the normed stream before the filter
     depth_terms: int = 0     # n > 0: what the layer hands on is sum_j c[j] X_j over the embedding's output X_0 and the
                              # results X_1 .. X_(n-1) of the layers so far, this one's last (names "depth": [n])
+    token_side: Optional[TokenSideSpec] = None   # "pre_norm": a gated slice of a second token table joins the stream last
 
 
 @dataclass(frozen=True)
@@ -344,6 +392,8 @@ class LayerCall:
     of owning one."""
     layer: int
     cache_of: Optional[int] = None
+    mix_in: bool = False     # before this call the stream becomes M [stream; embedding output] (ModelSpec.names["pass_in"]:
+                             # [width, 2 width]): how a pass over repeated layers starts
 
 
 @dataclass(frozen=True)
@@ -359,15 +409,34 @@ class ModelSpec:
     init_std: float = 0.02   # random-weights mode: matrices and tables ~ N(0, init_std)
     embed_scale: float = 1.0  # the embedding rows are multiplied by it (1: as stored, LFM3's)
     logit_cap: float = 0.0    # > 0: logits = cap * tanh(logits / cap) (0: none, LFM3's)
+    logit_scale: float = 1.0  # the logits are multiplied by it (positive, so that their order stays)
     prefixes: Tuple[str, ...] = ("model.",)   # tried in turn for "<prefix>embed_tokens.weight"
     ignorable: Tuple[str, ...] = ()           # regular expressions: tensors of a folder that match are neither needed nor refused
     embedding: Optional[object] = None        # a spec with a `kind` (registry.register_embedding); None: table[tok] * embed_scale
     depth_history: bool = False               # the step keeps every layer's result (layers with `depth_terms` read them)
     names: Dict[str, str] = field(default_factory=lambda: {
         "embed": "embed_tokens.weight", "final_norm": "embedding_norm.weight",
-        "head": "lm_head.weight"})   # "head" is looked up without the model prefix
+        "head": "lm_head.weight", "pass_in": "loop.in"})   # "head" is looked up without the model prefix
+
+    @property
+    def mixes_in(self) -> bool:
+        return any(c.mix_in for c in self.order)
+
+    def shared_tables(self) -> Dict[str, Tuple[int, int]]:
+        """Tensors at the model's top level that the layers read (name -> shape): the token-side tables."""
+        out: Dict[str, Tuple[int, int]] = {}
+        for layer in self.layers:
+            ts = getattr(layer, "token_side", None)
+            if ts is not None:
+                shape = (ts.vocab, ts.columns)
+                if out.setdefault(ts.table, shape) != shape:
+                    raise ValueError(f"layers disagree about the shape of '{ts.table}'")
+        return out
 
     def validate(self) -> None:
+        if not self.logit_scale > 0:
+            raise ValueError("logit_scale must be positive")
+        self.shared_tables()
         if not self.layers:
             raise ValueError("a model needs at least one layer")
         if not self.order:

@@ -233,10 +233,12 @@ __global__ void moe_route_warp_kernel(const float* __restrict__ logits, int ld, 
 // `group_top` largest choice scores, and only experts of the `keep` best groups can be chosen (the others count as minus
 // infinity, so negative choice scores still beat them). The `top` largest choice scores are chosen (ties: the lower index,
 // for groups and for experts); the weights are the chosen experts' s times `scale`, not normed to sum 1 unless `renorm`.
+// `score` 1: s is the softmax over all E logits instead of their sigmoids. Experts from `real` on have no weights (their
+// output is their input): a choice of one is written as id -1, with its weight.
 // A warp per token; the token's s and c stand in shared memory (2 E floats a warp).
 __global__ void moe_route_grouped_kernel(const float* __restrict__ logits, int ld, int T, int E, int top,
                                          const float* __restrict__ correction, int groups, int keep, int group_top, float scale,
-                                         int renorm, int32_t* __restrict__ ids, float* __restrict__ wts) {
+                                         int renorm, int score, int real, int32_t* __restrict__ ids, float* __restrict__ wts) {
     extern __shared__ float route_smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -247,8 +249,17 @@ __global__ void moe_route_grouped_kernel(const float* __restrict__ logits, int l
     float* c = s + E;
     float* gs = c + E;
     const float* z = logits + (int64_t)t * ld;
+    // score 1: the scores are the softmax over all E logits (largest first taken off, sum in the warp's fixed order)
+    float z_max = -INFINITY, z_sum = 1.0f;
+    if (score == 1) {
+        for (int e = lane; e < E; e += 32) z_max = fmaxf(z_max, z[e]);
+        z_max = warp_max(z_max);
+        z_sum = 0.0f;
+        for (int e = lane; e < E; e += 32) z_sum += expf(z[e] - z_max);
+        z_sum = warp_sum(z_sum);
+    }
     for (int e = lane; e < E; e += 32) {
-        const float v = 1.0f / (1.0f + expf(-z[e]));
+        const float v = score == 1 ? expf(z[e] - z_max) / z_sum : 1.0f / (1.0f + expf(-z[e]));
         s[e] = v;
         c[e] = v + (correction != nullptr ? correction[e] : 0.0f);
     }
@@ -319,7 +330,7 @@ __global__ void moe_route_grouped_kernel(const float* __restrict__ logits, int l
         }
     }
     if (lane < top) {
-        ids[(int64_t)t * top + lane] = mine_id;
+        ids[(int64_t)t * top + lane] = mine_id < real ? mine_id : -1;        // (an expert without weights: its input passes)
         wts[(int64_t)t * top + lane] = (renorm ? mine / sum : mine) * scale;
     }
 }
@@ -339,7 +350,8 @@ __global__ void moe_plan_kernel(const int32_t* __restrict__ ids, int n, int E, i
     if (pad)
         for (int i = threadIdx.x; i < rows_cap; i += blockDim.x) source[i] = -1;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        if (ids[i] >= 0) atomicAdd(&count[ids[i]], 1);      // (a row without an expert, id -1, takes no place)
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0, tiles = 0;
@@ -360,6 +372,10 @@ __global__ void moe_plan_kernel(const int32_t* __restrict__ ids, int n, int E, i
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        if (ids[i] < 0) {
+            place[i] = -1;
+            continue;
+        }
         const int p = atomicAdd(&next[ids[i]], 1);
         place[i] = p;
         source[p] = i;
@@ -483,7 +499,8 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, int64_t ldx16, co
 template <typename TI, typename TO>
 __global__ void moe_combine_kernel(const TI* __restrict__ rows_out, const int32_t* __restrict__ place,
                                    const float* __restrict__ wts, TO* __restrict__ y, int H, int top,
-                                   const TI* __restrict__ shared, const float* __restrict__ shared_gate, int ld_gate) {
+                                   const TI* __restrict__ shared, const float* __restrict__ shared_gate, int ld_gate,
+                                   const TI* __restrict__ passed, int64_t ld_passed) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -491,8 +508,12 @@ __global__ void moe_combine_kernel(const TI* __restrict__ rows_out, const int32_
     const float sg = shared == nullptr ? 0.0f : shared_gate == nullptr ? 1.0f : sigmoid_f(shared_gate[(int64_t)t * ld_gate]);
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float v = shared == nullptr ? 0.0f : sg * to_f32(shared[(int64_t)t * H + c]);
-        for (int k = 0; k < top; ++k)
-            v = fmaf(wts[(int64_t)t * top + k], to_f32(rows_out[(int64_t)place[(int64_t)t * top + k] * H + c]), v);
+        for (int k = 0; k < top; ++k) {
+            // (a choice without a place is an expert that hands its input through: `passed` holds the tokens' inputs)
+            const int pl = place[(int64_t)t * top + k];
+            const float r = pl >= 0 ? to_f32(rows_out[(int64_t)pl * H + c]) : passed != nullptr ? to_f32(passed[(int64_t)t * ld_passed + c]) : 0.0f;
+            v = fmaf(wts[(int64_t)t * top + k], r, v);
+        }
         y[(int64_t)t * H + c] = from_f32<TO>(v);
     }
 }
@@ -566,18 +587,21 @@ XS_API int xs_moe_route(const float* logits, int ld, int T, int E, int top, floa
 }
 
 XS_API int xs_moe_route_grouped(const float* logits, int ld, int T, int E, int top, const float* correction, int groups, int keep,
-                                int group_top, float scale, int renorm, int32_t* ids, float* wts, cudaStream_t stream) {
+                                int group_top, float scale, int renorm, int score, int real, int32_t* ids, float* wts,
+                                cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop && ld >= E,
                "moe_route_grouped: %d tokens, %d experts (row stride %d), top %d (at most %d)", T, E, ld, top, kMaxTop);
     XS_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && group_top > 0 && group_top <= 8,
                "moe_route_grouped: %d experts in %d groups of which %d are kept (a group's %d largest count)", E, groups, keep, group_top);
     XS_REQUIRE((int64_t)keep * (E / groups) >= top, "moe_route_grouped: %d groups of %d experts cannot give %d choices", keep, E / groups, top);
+    XS_REQUIRE((score == 0 || score == 1) && real > 0 && real <= E, "moe_route_grouped: score %d (0 sigmoid, 1 softmax), %d of %d experts with weights",
+               score, real, E);
     const size_t per_warp = (size_t)(2 * E + groups) * sizeof(float);
     XS_REQUIRE(per_warp <= 40 * 1024, "moe_route_grouped: %d experts are more than the kernel's shared memory holds", E);
     const int warps = per_warp * 4 <= 40 * 1024 ? 4 : 1;
     xs_launch(moe_route_grouped_kernel, dim3(ceil_div_i(T, warps)), dim3(32 * warps), per_warp * warps, stream, logits, ld, T, E, top,
-              correction, groups, keep, group_top, scale, renorm, ids, wts);
+              correction, groups, keep, group_top, scale, renorm, score, real, ids, wts);
     XS_LAUNCH_CHECK("moe_route_grouped");
     return 0;
 }
@@ -640,12 +664,14 @@ XS_API int xs_moe_gather(const void* x, int64_t ldx, const int32_t* source, int 
 }
 
 XS_API int xs_moe_combine(const void* rows_out, const int32_t* place, const float* wts, void* y, int T, int H, int top,
-                          const void* shared, const float* shared_gate, int ld_gate, int dtype, cudaStream_t stream) {
+                          const void* shared, const float* shared_gate, int ld_gate, const void* passed, int64_t ld_passed, int dtype,
+                          cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && H > 0 && top > 0, "moe_combine: %d tokens of %d, top %d", T, H, top);
     XS_DISPATCH_DTYPE(dtype, TT,
                       xs_launch(moe_combine_kernel<TT, TT>, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream,
-                                (const TT*)rows_out, place, wts, (TT*)y, H, top, (const TT*)shared, shared_gate, ld_gate));
+                                (const TT*)rows_out, place, wts, (TT*)y, H, top, (const TT*)shared, shared_gate, ld_gate,
+                                (const TT*)passed, ld_passed));
     XS_LAUNCH_CHECK("moe_combine");
     return 0;
 }

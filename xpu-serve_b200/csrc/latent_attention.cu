@@ -364,7 +364,7 @@ XS_API int xs_latent_prepare(const void* down, int64_t ld_down, const void* q, i
                              const int32_t* page_table, int P, void* pool, void* q_rot, int T, int H, int Dn, int Dr, int R,
                              int dims, int page_size, float eps, int write_kv, int dtype, cudaStream_t stream) {
     if (T == 0) return 0;
-    XS_REQUIRE(H > 0 && Dn > 0 && Dr > 0 && R > 0, "latent_prepare: %d heads of %d + %d, rank %d", H, Dn, Dr, R);
+    XS_REQUIRE(H > 0 && Dn > 0 && Dr >= 0 && R > 0, "latent_prepare: %d heads of %d + %d, rank %d", H, Dn, Dr, R);
     XS_REQUIRE(dims >= 0 && dims % 2 == 0 && dims <= Dr, "latent_prepare: %d rotated channels of %d", dims, Dr);
     XS_REQUIRE(!write_kv || (pool != nullptr && page_table != nullptr && P > 0), "latent_prepare: no cache to write to");
     const int turned = table != nullptr ? dims : 0;
@@ -390,7 +390,7 @@ XS_API int xs_latent_attention_generic(const void* q_lat, int64_t qs_t, int64_t 
                                        void* out, int64_t os_t, int64_t os_h, int T, int H, int R, int Dr, int page_size,
                                        float scale, int window, int dtype, cudaStream_t stream) {
     if (T == 0) return 0;
-    XS_REQUIRE(H > 0 && R > 0 && R <= kMaxRank && Dr > 0, "latent attention: %d heads, rank %d (at most %d), %d rotated", H, R,
+    XS_REQUIRE(H > 0 && R > 0 && R <= kMaxRank && Dr >= 0, "latent attention: %d heads, rank %d (at most %d), %d rotated", H, R,
                kMaxRank, Dr);
     XS_REQUIRE(window >= 0 && page_size > 0 && P > 0, "latent attention: window %d, page size %d, %d pages", window, page_size, P);
     const int warps = 4;
@@ -920,7 +920,7 @@ __global__ void latent_attention_combine_kernel(const float* __restrict__ scratc
 }  // namespace
 
 XS_API int xs_latent_attention_mma_supports(int R, int Dr, int page_size) {
-    return R >= 16 && R % 8 == 0 && Dr >= 8 && Dr % 8 == 0 && R <= 512 && page_size == 64 &&
+    return R >= 16 && R % 8 == 0 && Dr >= 0 && Dr % 8 == 0 && R <= 512 && page_size == 64 &&
            (size_t)(2 * 64 * (((R + Dr + 15) & ~15) + 8) * 2 + 4 * 16 * 72 * 2 + 2 * 64 * 4) <= 227 * 1024;
 }
 

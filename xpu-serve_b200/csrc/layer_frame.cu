@@ -1,6 +1,6 @@
 // Pieces of a layer's frame that are neither a product nor a mixer:
 //
-//   embed_pos          h[t] = table[id[t]] + rows[position[t]]: a token table plus a learned row per position
+//   embed_pos          h[t] = table[id[t]] * scale + rows[position[t]]: a token table plus a learned row per position
 //   causal_conv        y[t, c] = (x[t, c] if residual) + act(sum_j taps[c, j] x[t - (n - 1) + j, c]) over a sequence's earlier
 //                      tokens, the inputs before a step coming from the sequence's state [n - 1, C], which then moves on
 //   gated_add          h[t, c] += branch[t, c] * sigmoid(logit[t, c] + bias[c]): a branch joins the float32 stream through
@@ -9,6 +9,11 @@
 //                      and every earlier layer's results
 //   rmsnorm_accumulate acc[t, :] (+)= scale * x[t, :] / sqrt(mean(x[t, :]^2) + eps) * w: branches that run side by side are
 //                      normed and summed in float32
+//   token_side         h[t] += unit_rms(P (gelu(G h[t]) * e[id[t]])) * w: a slice of a second token table, gated by the
+//                      stream, joins it through a small projection and a norm (a pending branch is added to h first)
+//   rmsnorm_rows       y[t, :n] = x[t, :n] / sqrt(mean(x[t, :n]^2) + eps) * w over columns of a wider matrix
+//   sigmoid_mul        o[t, c] *= sigmoid(g[t, c])
+//   cast_rows          dst[t, :n] = src[t, :n] (float32 to the activation type) into columns of a wider matrix
 //
 // All sums are float32 in a fixed order per element, whatever else is in the batch.
 #include <math.h>
@@ -22,14 +27,97 @@ constexpr int kMaxTerms = 512;
 
 template <typename T>
 __global__ void embed_pos_kernel(const T* __restrict__ table, const T* __restrict__ rows, const int32_t* __restrict__ ids,
-                                 const int32_t* __restrict__ positions, float* __restrict__ h, int H) {
+                                 const int32_t* __restrict__ positions, float* __restrict__ h, int H, float scale) {
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const int64_t id = ids[t], pos = positions[t];
     pdl_wait();
     const T* a = table + id * H;
     const T* b = rows + pos * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) h[(int64_t)t * H + c] = to_f32(a[c]) + to_f32(b[c]);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) h[(int64_t)t * H + c] = fmaf(to_f32(a[c]), scale, to_f32(b[c]));
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// One block a token. h: the float32 stream [T, W]; m: a branch still to be added (or null); table: [vocab, ld_table] of
+// which columns [off, off + d) are this layer's; gate_w [d, W], proj_w [W, d] in the matrices' type; norm_w [W] float32.
+template <typename T, typename TM>
+__global__ void token_side_kernel(float* __restrict__ h, const TM* __restrict__ m, const int32_t* __restrict__ ids,
+                                  const T* __restrict__ table, int64_t ld_table, int off, int d, const T* __restrict__ gate_w,
+                                  const T* __restrict__ proj_w, const float* __restrict__ norm_w, int W, float eps) {
+    extern __shared__ float side_smem[];
+    __shared__ float scratch[32];
+    float* hs = side_smem;               // [W] the stream's row
+    float* ys = hs + W;                  // [W] the projection's output
+    float* gs = ys + W;                  // [d]
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int64_t id = ids[t];
+    pdl_wait();
+    float* hr = h + (int64_t)t * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) hs[c] = hr[c] + (m != nullptr ? to_f32(m[(int64_t)t * W + c]) : 0.0f);
+    __syncthreads();
+    for (int j = warp; j < d; j += warps) {
+        const T* gw = gate_w + (int64_t)j * W;
+        float acc = 0.0f;
+        for (int c = lane; c < W; c += 32) acc = fmaf(to_f32(gw[c]), hs[c], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) gs[j] = gelu_tanh_f(acc) * to_f32(table[id * ld_table + off + j]);
+    }
+    __syncthreads();
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const T* pw = proj_w + (int64_t)c * d;
+        float acc = 0.0f;
+        for (int j = 0; j < d; ++j) acc = fmaf(to_f32(pw[j]), gs[j], acc);
+        ys[c] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) hr[c] = hs[c] + ys[c] * inv * norm_w[c];
+}
+
+template <typename T>
+__global__ void rmsnorm_rows_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ w, T* __restrict__ y,
+                                    int64_t ldy, int n, float eps) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* xr = x + (int64_t)blockIdx.x * ldx;
+    T* yr = y + (int64_t)blockIdx.x * ldy;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float v = to_f32(xr[c]);
+        ss = fmaf(v, v, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) yr[c] = from_f32<T>(to_f32(xr[c]) * inv * w[c]);
+}
+
+template <typename T>
+__global__ void sigmoid_mul_kernel(T* __restrict__ o, int64_t ldo, const T* __restrict__ g, int64_t ldg, int64_t total, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / n;
+        const int c = (int)(i - t * n);
+        const float gv = to_f32(g[t * ldg + c]);
+        o[t * ldo + c] = from_f32<T>(to_f32(o[t * ldo + c]) / (1.0f + expf(-gv)));
+    }
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ src, int64_t lds, T* __restrict__ dst, int64_t ldd, int64_t total, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / n;
+        const int c = (int)(i - t * n);
+        dst[t * ldd + c] = from_f32<T>(src[t * lds + c]);
+    }
 }
 
 // SiLU of a filter's sum. In front of a rounding to bfloat16 the fast exponential and division do (a few units in the last
@@ -271,12 +359,69 @@ __global__ void rmsnorm_accumulate_kernel(const T* __restrict__ x, const float* 
 }  // namespace
 
 XS_API int xs_embed_pos(const void* table, const void* rows, int dtype, const int32_t* ids, const int32_t* positions, float* h,
-                        int T, int H, cudaStream_t stream) {
+                        int T, int H, float scale, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && H > 0, "embed_pos: %d tokens of width %d", T, H);
     XS_DISPATCH_DTYPE(dtype, TT, xs_launch(embed_pos_kernel<TT>, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, (const TT*)table,
-                                           (const TT*)rows, ids, positions, h, H));
+                                           (const TT*)rows, ids, positions, h, H, scale));
     XS_LAUNCH_CHECK("embed_pos");
+    return 0;
+}
+
+// h [T, W] float32; m: a branch [T, W] that joins h first (element type m_dtype), or null; table [vocab, ld_table], gate_w
+// [d, W] and proj_w [W, d] in the element type `dtype`; norm_w [W] float32.
+XS_API int xs_token_side(float* h, const void* m, int m_dtype, const int32_t* ids, const void* table, int64_t ld_table, int off,
+                         int d, const void* gate_w, const void* proj_w, const float* norm_w, int T, int W, float eps, int dtype,
+                         cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && W > 0 && d > 0 && off >= 0 && off + d <= ld_table, "token_side: %d tokens of %d, columns %d + %d of %lld", T, W,
+               off, d, (long long)ld_table);
+    const size_t smem = (size_t)(2 * W + d) * sizeof(float);
+    XS_REQUIRE(smem <= 200 * 1024, "token_side: width %d with %d side channels does not fit shared memory", W, d);
+#define XS_GO(TT, TM)                                                                                                  \
+    do {                                                                                                               \
+        if (smem > 48 * 1024)                                                                                          \
+            cudaFuncSetAttribute(token_side_kernel<TT, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        xs_launch(token_side_kernel<TT, TM>, dim3(T), dim3(W >= 1024 ? 256 : 128), smem, stream, h, (const TM*)m, ids,  \
+                  (const TT*)table, ld_table, off, d, (const TT*)gate_w, (const TT*)proj_w, norm_w, W, eps);           \
+    } while (0)
+    XS_DISPATCH_DTYPE(dtype, TT, do {
+        if (m_dtype == XS_BF16) XS_GO(TT, __nv_bfloat16);
+        else XS_GO(TT, float);
+    } while (0));
+#undef XS_GO
+    XS_LAUNCH_CHECK("token_side");
+    return 0;
+}
+
+XS_API int xs_rmsnorm_rows(const void* x, int64_t ldx, const float* w, void* y, int64_t ldy, int T, int n, float eps, int dtype,
+                           cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && n > 0 && ldx >= n && ldy >= n, "rmsnorm_rows: %d rows of %d", T, n);
+    XS_DISPATCH_DTYPE(dtype, TT, xs_launch(rmsnorm_rows_kernel<TT>, dim3(T), dim3(n >= 1024 ? 256 : 128), 0, stream, (const TT*)x, ldx,
+                                           w, (TT*)y, ldy, n, eps));
+    XS_LAUNCH_CHECK("rmsnorm_rows");
+    return 0;
+}
+
+XS_API int xs_sigmoid_mul(void* o, int64_t ldo, const void* g, int64_t ldg, int T, int n, int dtype, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && n > 0 && ldo >= n && ldg >= n, "sigmoid_mul: %d rows of %d", T, n);
+    const int64_t total = (int64_t)T * n;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    XS_DISPATCH_DTYPE(dtype, TT, xs_launch(sigmoid_mul_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (TT*)o, ldo, (const TT*)g, ldg,
+                                           total, n));
+    XS_LAUNCH_CHECK("sigmoid_mul");
+    return 0;
+}
+
+XS_API int xs_cast_rows(const float* src, int64_t lds, void* dst, int64_t ldd, int T, int n, int dtype, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && n > 0 && lds >= n && ldd >= n, "cast_rows: %d rows of %d", T, n);
+    const int64_t total = (int64_t)T * n;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    XS_DISPATCH_DTYPE(dtype, TT, xs_launch(cast_rows_kernel<TT>, dim3(blocks), dim3(256), 0, stream, src, lds, (TT*)dst, ldd, total, n));
+    XS_LAUNCH_CHECK("cast_rows");
     return 0;
 }
 

@@ -114,6 +114,12 @@ __global__ void logit_cap_kernel(float* __restrict__ logits, int64_t n, float ca
         logits[i] = cap * tanhf(logits[i] * inv_cap);
 }
 
+__global__ void logit_scale_kernel(float* __restrict__ logits, int64_t n, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) logits[i] *= scale;
+}
+
 XS_API int xs_embed(const void* table, int table_dtype, const int32_t* ids, float* h, int T, int H, float scale,
                     cudaStream_t stream) {
     if (T == 0) return 0;
@@ -143,6 +149,16 @@ XS_API int xs_embed_pair(const void* table, const void* pair, int table_dtype, c
     XS_DISPATCH_DTYPE(table_dtype, TW, XS_GO(TW));
 #undef XS_GO
     XS_LAUNCH_CHECK("embed_pair");
+    return 0;
+}
+
+// logits *= scale, in place: a constant that some architectures put between the head and the softmax.
+XS_API int xs_logit_scale(float* logits, int64_t n, float scale, cudaStream_t stream) {
+    if (n == 0) return 0;
+    XS_REQUIRE(n > 0, "logit scale: %lld values", (long long)n);
+    const int blocks = (int)(n / 1024 < 1 ? 1 : (n / 1024 > 1184 ? 1184 : n / 1024));
+    xs_launch(logit_scale_kernel, dim3(blocks), dim3(256), 0, stream, logits, n, scale);
+    XS_LAUNCH_CHECK("logit_scale");
     return 0;
 }
 
@@ -375,9 +391,13 @@ XS_API int xs_add_rmsnorm(float* h, const void* m, int m_dtype, const float* pos
 // Layout of a gate/up row: interleave 0: [F gate | F up]; interleave 8: blocks of 16 columns,
 // 8 gate then the 8 up of the same f (how the stacked weight is ordered for the fused epilogue
 // of the few-row product).
+// ACT 1: the gate's activation is the tanh form of gelu instead, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float gelu_tanh_f(float g) { return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))); }
+template <int ACT>
+__device__ __forceinline__ float gate_act_f(float g) { return ACT == 1 ? gelu_tanh_f(g) : silu_f(g); }
 
-template <typename T>
+template <typename T, int ACT>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int F, int64_t ld,
                                 int interleave) {
     pdl_launch_dependents();
@@ -387,11 +407,12 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
         const int f = (int)(i - t * F);
         const int64_t gi = interleave ? (int64_t)(f / interleave) * 2 * interleave + f % interleave : f;
         const int64_t ui = interleave ? gi + interleave : (int64_t)F + f;
-        out[i] = from_f32<T>(silu_f(to_f32(gu[t * ld + gi])) * to_f32(gu[t * ld + ui]));
+        out[i] = from_f32<T>(gate_act_f<ACT>(to_f32(gu[t * ld + gi])) * to_f32(gu[t * ld + ui]));
     }
 }
 
 // 8 outputs a thread, 16-byte loads and stores; F a multiple of 8, rows 16-byte aligned.
+template <int ACT>
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                        int64_t total8, int F8, int64_t ld, int interleave) {
     pdl_launch_dependents();
@@ -409,30 +430,44 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __n
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const float2 gf = __bfloat1622float2(gp[k]), uf = __bfloat1622float2(up[k]);
-            op[k] = __floats2bfloat162_rn(silu_f(gf.x) * uf.x, silu_f(gf.y) * uf.y);
+            op[k] = __floats2bfloat162_rn(gate_act_f<ACT>(gf.x) * uf.x, gate_act_f<ACT>(gf.y) * uf.y);
         }
         *reinterpret_cast<uint4*>(out + t * 8 * (int64_t)F8 + 8 * j) = o;
     }
 }
 
-XS_API int xs_silu_mul(const void* gu, void* out, int dtype, int T, int F, int64_t ld, int interleave,
-                       cudaStream_t stream) {
+// act 0: silu(gate) * up; 1: gelu_tanh(gate) * up.
+XS_API int xs_gated_act(const void* gu, void* out, int dtype, int T, int F, int64_t ld, int interleave, int act,
+                        cudaStream_t stream) {
     if (T == 0) return 0;
-    XS_REQUIRE(T > 0 && F > 0 && ld >= 2 * (int64_t)F, "silu_mul: %d rows, %d columns, stride %lld", T, F, (long long)ld);
-    XS_REQUIRE(interleave == 0 || (interleave == 8 && F % 8 == 0), "silu_mul: interleave %d with %d columns", interleave, F);
+    XS_REQUIRE(T > 0 && F > 0 && ld >= 2 * (int64_t)F, "gated_act: %d rows, %d columns, stride %lld", T, F, (long long)ld);
+    XS_REQUIRE(interleave == 0 || (interleave == 8 && F % 8 == 0), "gated_act: interleave %d with %d columns", interleave, F);
+    XS_REQUIRE(act == 0 || act == 1, "gated_act: activation code %d (0 silu, 1 gelu_tanh)", act);
     if (dtype == XS_BF16 && F % 8 == 0 && ld % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0) {
         const int64_t total8 = (int64_t)T * (F / 8);
         const int blocks = (int)((total8 + 255) / 256 < 148 * 32 ? (total8 + 255) / 256 : 148 * 32);
-        xs_launch(silu_mul_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
-                  (__nv_bfloat16*)out, total8, F / 8, ld, interleave);
-        XS_LAUNCH_CHECK("silu_mul");
+        if (act == 1)
+            xs_launch(silu_mul_bf16x8_kernel<1>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                      total8, F / 8, ld, interleave);
+        else
+            xs_launch(silu_mul_bf16x8_kernel<0>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                      total8, F / 8, ld, interleave);
+        XS_LAUNCH_CHECK("gated_act");
         return 0;
     }
     const int64_t total = (int64_t)T * F;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    XS_DISPATCH_DTYPE(dtype, TT, xs_launch(silu_mul_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (const TT*)gu, (TT*)out, total, F, ld, interleave));
-    XS_LAUNCH_CHECK("silu_mul");
+    XS_DISPATCH_DTYPE(dtype, TT, do {
+        if (act == 1) xs_launch(silu_mul_kernel<TT, 1>, dim3(blocks), dim3(256), 0, stream, (const TT*)gu, (TT*)out, total, F, ld, interleave);
+        else xs_launch(silu_mul_kernel<TT, 0>, dim3(blocks), dim3(256), 0, stream, (const TT*)gu, (TT*)out, total, F, ld, interleave);
+    } while (0));
+    XS_LAUNCH_CHECK("gated_act");
     return 0;
+}
+
+XS_API int xs_silu_mul(const void* gu, void* out, int dtype, int T, int F, int64_t ld, int interleave,
+                       cudaStream_t stream) {
+    return xs_gated_act(gu, out, dtype, T, F, ld, interleave, 0, stream);
 }
 
 // ------------------------------------------------------------ zero state rows

@@ -25,7 +25,7 @@ from ..cache import Cache, CacheError
 from ..config.json_util import ConfigError, read_json
 from ..config.spec import ModelSpec
 from ..ops import lib as ops
-from ..parts.block import ResidualStream
+from ..parts.block import SHARED, ResidualStream
 from ..weights.loader import load_weights
 from .runtime import Runtime, Workspace
 from .step import StepContext, StepStager
@@ -90,8 +90,13 @@ class Model:
         self.head = self.embed if spec.tied_head else rt.matrix(weights[spec.names["head"]])
         self.final_norm = registry.norm_class(spec.final_norm.kind)(spec.final_norm, weights, spec.names["final_norm"], rt)
         self.blocks: List[object] = []
+        # tables at the model's top level that layers read (each layer finds them under parts.block.SHARED + name)
+        tables = {SHARED + name: weights[name] for name in spec.shared_tables()}
+        # the matrix that mixes the stream with the embedding's output in front of a pass over repeated layers
+        self.pass_in = rt.matrix(weights[spec.names["pass_in"]]) if spec.mixes_in else None
         for layer in spec.layers:
             own = {k[len(layer.prefix):]: v for k, v in weights.items() if k.startswith(layer.prefix)}
+            own.update(tables)
             self.blocks.append(registry.arrangement_class(layer.kind)(layer, own, rt))
         # an embedding that is more than a table lookup is a part of its own; what it keeps per sequence is the cache's
         # last view, behind the layer calls'
@@ -381,10 +386,23 @@ class Model:
             # every layer's result is kept for the layers that hand on a weighted sum of them (parts/block.py); the stream
             # then lives in the history's planes, one further per layer, and one more takes the last layer's sum
             stream.keep_history(rt.ws.get("depth_history", (len(spec.order) + 2, ctx.n_tokens, spec.hidden), torch.float32))
+        pair = None
+        if self.pass_in is not None:
+            # [stream | embedding output] in the activation type: the right half is written once a step, the left half in
+            # front of every pass, and one product with the mixing matrix gives the pass's stream (float32)
+            pair = rt.ws.get("pass_pair", (ctx.n_tokens, 2 * spec.hidden), rt.act_dtype)
+            ops.cast_rows(h, pair[:, spec.hidden:])
         last = len(spec.order) - 1
+        passes = 0
         for i, call in enumerate(spec.order):
-            # the norm that reads the stream after this block, for products that carry the norm with them
-            next_norm = self.blocks[spec.order[i + 1].layer].first_norm if i < last else self.final_norm
+            if call.mix_in:
+                stream.flush(self.final_norm)
+                ops.cast_rows(stream.h, pair[:, :spec.hidden])
+                passes += 1
+                stream.replace(rt.linear(pair, self.pass_in, f"stream_pass{passes & 1}", out_dtype=torch.float32))
+            # the norm that reads the stream after this block, for products that carry the norm with them (none across a
+            # mix, which rewrites the stream)
+            next_norm = self.final_norm if i == last else None if spec.order[i + 1].mix_in else self.blocks[spec.order[i + 1].layer].first_norm
             self.blocks[call.layer].forward(stream, ctx, cache.views[i], next_norm)
         if ctx.want_rows.numel() == 0:
             stream.flush(self.final_norm)
@@ -396,6 +414,8 @@ class Model:
         logits = rt.linear(y, self.head, "logits", out_dtype=torch.float32, argmax_into=greedy)
         if spec.logit_cap > 0.0:
             ops.logit_cap(logits, spec.logit_cap)
+        if spec.logit_scale != 1.0:
+            ops.logit_scale(logits, spec.logit_scale)
         return logits
 
 

@@ -35,6 +35,13 @@ def _signatures(lib) -> None:
         "xs_logit_cap": [P, L, F, P],
         "xs_add_rmsnorm": [P, P, I, P, P, P, I, P, I, I, F, F, P],
         "xs_silu_mul": [P, P, I, I, I, L, I, P],
+        "xs_gated_act": [P, P, I, I, I, L, I, I, P],
+        "xs_logit_scale": [P, L, F, P],
+        "xs_token_side": [P, P, I, P, P, L, I, I, P, P, P, I, I, F, I, P],
+        "xs_rmsnorm_rows": [P, L, P, P, L, I, I, F, I, P],
+        "xs_sigmoid_mul": [P, L, P, L, I, I, I, P],
+        "xs_cast_rows": [P, L, P, L, I, I, I, P],
+        "xs_lightning_scan": [P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, P, P, I, P, P],
         "xs_zero_rows": [P, P, I, L, P],
         "xs_gemm_generic": [P, P, P, P, I, I, I, I, I, L, L, L, P],
         "xs_qk_norm_rope_store": [P, L, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P],
@@ -63,7 +70,7 @@ def _signatures(lib) -> None:
         "xs_moe_gather": [P, L, P, I, P, I, I, P],
         "xs_gemm_tc_grouped": [P, P, P, I, I, P, I, I, I, I, I, L, L, F, F, F, P, P],
         "xs_moe_gemm": [P, L, P, P, L, P, I, P, I, I, I, I, F, F, F, I, I, P],
-        "xs_moe_combine": [P, P, P, P, I, I, I, P, P, I, I, P],
+        "xs_moe_combine": [P, P, P, P, I, I, I, P, P, I, P, L, I, P],
         "xs_relu_squared": [P, P, I, L, P],
         "xs_embed_pair": [P, P, I, P, P, P, P, P, P, P, P, P, I, I, F, I, ctypes.c_longlong, ctypes.c_longlong, F, P],
         "xs_mlstm_scan": [P, L, I, I, I, P, L, P, P, P, P, P, P, P, I, I, I, I, F, F, I, P, P, I, P, P, P],
@@ -72,13 +79,13 @@ def _signatures(lib) -> None:
         "xs_gemm_batched": [P, L, L, P, L, L, P, L, L, I, I, I, I, I, P],
         "xs_latent_attention_mma": [P, L, L, P, P, P, I, P, P, P, L, P, P, L, L, P, L, I, I, I, I, I, I, I, F, I, I, P],
         "xs_mamba2_conv": [P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P],
-        "xs_embed_pos": [P, P, I, P, P, P, I, I, P],
+        "xs_embed_pos": [P, P, I, P, P, P, I, I, F, P],
         "xs_causal_conv": [P, L, P, P, P, P, P, P, L, I, I, I, I, I, I, I, I, P],
         "xs_gated_add": [P, P, I, P, L, P, I, I, P],
         "xs_depth_average": [P, L, P, I, P, L, P],
         "xs_rmsnorm_accumulate": [P, I, P, P, I, I, F, F, I, P],
         "xs_gated_delta_scan": [P, L, I, I, I, P, L, P, P, P, P, P, P, I, I, I, I, I, F, F, I, I, P],
-        "xs_moe_route_grouped": [P, I, I, I, I, P, I, I, I, F, I, P, P, P],
+        "xs_moe_route_grouped": [P, I, I, I, I, P, I, I, I, F, I, I, I, P, P, P],
         "xs_mamba2_scan": [P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_mamba2_scan_chunked": [P, P, L, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     }
@@ -330,6 +337,29 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> None:
     if gu.shape[0] != T or gu.shape[1] < 2 * F:
         raise KernelError(f"gate_up is {tuple(gu.shape)} for an output of {tuple(out.shape)}")
     _check(load().xs_silu_mul(gu.data_ptr(), out.data_ptr(), _code(gu), T, F, gu.stride(0), int(interleave), _stream()))
+
+
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(gu: torch.Tensor, out: torch.Tensor, act: str = "silu", interleave: int = 0) -> None:
+    """out = act(gate) * up with act "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))); the layouts
+    of `silu_mul`."""
+    if act not in GATE_ACTS:
+        raise KernelError(f"gated_act: activation '{act}' ({', '.join(GATE_ACTS)})")
+    _need(out, "out", gu.dtype)
+    if not gu.is_cuda or gu.dim() != 2 or gu.stride(1) != 1:
+        raise KernelError("gate_up must be a CUDA matrix with contiguous rows")
+    T, F = out.shape
+    if gu.shape[0] != T or gu.shape[1] < 2 * F:
+        raise KernelError(f"gate_up is {tuple(gu.shape)} for an output of {tuple(out.shape)}")
+    _check(load().xs_gated_act(gu.data_ptr(), out.data_ptr(), _code(gu), T, F, gu.stride(0), int(interleave), GATE_ACTS[act], _stream()))
+
+
+def logit_scale(logits: torch.Tensor, scale: float) -> None:
+    """logits *= scale, in place."""
+    _need(logits, "logits", torch.float32)
+    _check(load().xs_logit_scale(logits.data_ptr(), logits.numel(), float(scale), _stream()))
 
 
 def zero_rows(state: torch.Tensor, slots: torch.Tensor) -> None:
@@ -877,12 +907,16 @@ def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tens
 
 def moe_route_grouped(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor, experts: Optional[int] = None,
                       correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1, group_top: int = 2,
-                      scale: float = 1.0, renorm: bool = False) -> None:
+                      scale: float = 1.0, renorm: bool = False, score: str = "sigmoid", real: Optional[int] = None) -> None:
     """Per row of float32 logits: scores s = sigmoid(logit), choice scores c = s + correction; the experts stand in
     `groups` equal groups of neighbours, of which the `keep` with the largest sum of their `group_top` largest choice
     scores stay open; the `top` open experts with the largest c (ties: the lower index) go into ids, their s (times
-    `scale`; divided by their sum with `renorm`) into wts."""
+    `scale`; divided by their sum with `renorm`) into wts. `score` "softmax": s is the softmax over all `experts` logits
+    instead. `real`: only the first so many experts have weights; a choice of a later one is written as id -1 (its input
+    passes, times its weight)."""
     _need(logits, "router logits", torch.float32); _need(ids, "ids", torch.int32); _need(wts, "weights", torch.float32)
+    if score not in ("sigmoid", "softmax"):
+        raise KernelError(f"moe_route_grouped: score '{score}' (sigmoid, softmax)")
     T, ld = logits.shape
     E = ld if experts is None else int(experts)
     if correction is not None:
@@ -892,7 +926,8 @@ def moe_route_grouped(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: to
     if ids.numel() < T * top or wts.numel() < T * top:
         raise KernelError(f"moe_route_grouped: {T} tokens x top {top} do not fit ids {ids.numel()} / weights {wts.numel()}")
     _check(load().xs_moe_route_grouped(logits.data_ptr(), ld, T, E, int(top), _ptr(correction), int(groups), int(keep),
-                                       int(group_top), float(scale), 1 if renorm else 0, ids.data_ptr(), wts.data_ptr(), _stream()))
+                                       int(group_top), float(scale), 1 if renorm else 0, 1 if score == "softmax" else 0,
+                                       E if real is None else int(real), ids.data_ptr(), wts.data_ptr(), _stream()))
 
 
 def moe_max_tiles_of(rows: int, experts: int, tile_rows: int) -> int:
@@ -966,13 +1001,17 @@ def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Te
 
 
 def moe_combine(rows_out: torch.Tensor, place: torch.Tensor, wts: torch.Tensor, y: torch.Tensor, top: int,
-                shared: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
+                shared: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None,
+                passed: Optional[torch.Tensor] = None) -> None:
     """y[t] = sum_k wts[t, k] * rows_out[place[t, k]], summed in float32 in the order of k. `shared` [T, H] (a unit that
     every token uses) starts the sum, times sigmoid(shared_gate[t, 0]) when `shared_gate` (float32, one row a token whose
-    first column is the gate's logit) is given."""
+    first column is the gate's logit) is given. `passed` [T, H] (the tokens' inputs): a choice whose place is -1 adds its
+    weight times the token's input (an expert that hands its input through)."""
     _need(rows_out, "expert outputs", y.dtype); _need(y, "y")
     T, H = y.shape
     ld_gate = 0
+    if passed is not None and (passed.dtype != y.dtype or passed.stride(1) != 1 or tuple(passed.shape) != (T, H)):
+        raise KernelError(f"moe_combine: passed inputs {tuple(passed.shape)} {passed.dtype} for y {tuple(y.shape)}")
     if shared is not None:
         _need(shared, "shared unit's output", y.dtype)
         if tuple(shared.shape) != (T, H):
@@ -982,7 +1021,8 @@ def moe_combine(rows_out: torch.Tensor, place: torch.Tensor, wts: torch.Tensor, 
                 raise KernelError(f"moe_combine: gate logits {tuple(shared_gate.shape)} {shared_gate.dtype} for {T} tokens")
             ld_gate = shared_gate.stride(0)
     _check(load().xs_moe_combine(rows_out.data_ptr(), place.data_ptr(), wts.data_ptr(), y.data_ptr(), T, H, int(top),
-                                 _ptr(shared), _ptr(shared_gate) if shared is not None else None, ld_gate, _code(y), _stream()))
+                                 _ptr(shared), _ptr(shared_gate) if shared is not None else None, ld_gate, _ptr(passed),
+                                 0 if passed is None else passed.stride(0), _code(y), _stream()))
 
 
 def relu_squared(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -1225,15 +1265,93 @@ def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: tor
 
 
 # ------------------------------------------------------------------------- a layer's frame
-def embed_pos(table: torch.Tensor, rows: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, h: torch.Tensor) -> None:
-    """h[t] = table[ids[t]] + rows[positions[t]], float32."""
+def embed_pos(table: torch.Tensor, rows: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, h: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """h[t] = table[ids[t]] * scale + rows[positions[t]], float32."""
     _need(table, "embedding table"); _need(rows, "position rows", table.dtype); _need(ids, "ids", torch.int32)
     _need(positions, "positions", torch.int32); _need(h, "h", torch.float32)
     T, H = h.shape
     if table.shape[1] != H or rows.shape[1] != H:
         raise KernelError(f"embed_pos: table {tuple(table.shape)}, rows {tuple(rows.shape)}, h {tuple(h.shape)}")
     _check(load().xs_embed_pos(table.data_ptr(), rows.data_ptr(), _code(table), ids.data_ptr(), positions.data_ptr(),
-                               h.data_ptr(), T, H, _stream()))
+                               h.data_ptr(), T, H, float(scale), _stream()))
+
+
+def token_side(h: torch.Tensor, branch: Optional[torch.Tensor], ids: torch.Tensor, table: torch.Tensor, offset: int, dim: int,
+               gate_w: torch.Tensor, proj_w: torch.Tensor, norm_w: torch.Tensor, eps: float) -> None:
+    """h += branch (when given); then h[t] += unit_rms(proj_w (gelu_tanh(gate_w h[t]) * table[ids[t], offset : offset + dim]))
+    * norm_w. h float32 [T, W]; table [vocab, *], gate_w [dim, W], proj_w [W, dim] of one element type; sums float32."""
+    _need(h, "h", torch.float32); _need(ids, "ids", torch.int32); _need(table, "side table")
+    _need(gate_w, "side gate", table.dtype); _need(proj_w, "side projection", table.dtype); _need(norm_w, "side norm", torch.float32)
+    T, W = h.shape
+    if tuple(gate_w.shape) != (dim, W) or tuple(proj_w.shape) != (W, dim) or norm_w.numel() != W or table.dim() != 2 \
+            or offset < 0 or offset + dim > table.shape[1] or ids.numel() < T:
+        raise KernelError(f"token_side: h {tuple(h.shape)}, gate {tuple(gate_w.shape)}, proj {tuple(proj_w.shape)}, "
+                          f"columns {offset} + {dim} of a table {tuple(table.shape)}")
+    if branch is not None:
+        _need(branch, "branch")
+        if tuple(branch.shape) != (T, W):
+            raise KernelError(f"token_side: branch {tuple(branch.shape)} for h {tuple(h.shape)}")
+    _check(load().xs_token_side(h.data_ptr(), _ptr(branch), F32 if branch is None else _code(branch), ids.data_ptr(),
+                                table.data_ptr(), table.stride(0), int(offset), int(dim), gate_w.data_ptr(), proj_w.data_ptr(),
+                                norm_w.data_ptr(), T, W, float(eps), _code(table), _stream()))
+
+
+def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, eps: float) -> None:
+    """y[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w for views x, y [T, n] (any row strides, contiguous columns) of one element
+    type; the sum and the scale in float32."""
+    _need(w, "w", torch.float32)
+    T, n = x.shape
+    if not x.is_cuda or x.stride(1) != 1 or y.stride(1) != 1 or tuple(y.shape) != (T, n) or y.dtype != x.dtype or w.numel() != n:
+        raise KernelError(f"rmsnorm_rows: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    _check(load().xs_rmsnorm_rows(x.data_ptr(), x.stride(0), w.data_ptr(), y.data_ptr(), y.stride(0), T, n, float(eps), _code(x), _stream()))
+
+
+def sigmoid_mul(o: torch.Tensor, g: torch.Tensor) -> None:
+    """o *= sigmoid(g), elementwise over views [T, n] (any row strides, contiguous columns) of one element type."""
+    T, n = o.shape
+    if not o.is_cuda or o.stride(1) != 1 or g.stride(1) != 1 or tuple(g.shape) != (T, n) or g.dtype != o.dtype:
+        raise KernelError(f"sigmoid_mul: o {tuple(o.shape)} {o.dtype}, g {tuple(g.shape)} {g.dtype}")
+    _check(load().xs_sigmoid_mul(o.data_ptr(), o.stride(0), g.data_ptr(), g.stride(0), T, n, _code(o), _stream()))
+
+
+def cast_rows(src: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst = src for views [T, n] (any row strides, contiguous columns): float32 into dst's element type."""
+    _need(src, "src", torch.float32)
+    T, n = src.shape
+    if src.dim() != 2 or src.stride(1) != 1 or dst.stride(1) != 1 or tuple(dst.shape) != (T, n):
+        raise KernelError(f"cast_rows: src {tuple(src.shape)}, dst {tuple(dst.shape)}")
+    _check(load().xs_cast_rows(src.data_ptr(), src.stride(0), dst.data_ptr(), dst.stride(0), T, n, _code(dst), _stream()))
+
+
+def lightning_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
+                   cu_seqlens: torch.Tensor, slots: torch.Tensor, y: torch.Tensor, heads: int, dim: int, vdim: int,
+                   chunks=None) -> None:
+    """The decayed linear recurrence S <- decay_h S + k v^T, o = S^T q over a step's tokens, sequence by sequence from each
+    slot's state (csrc/lightning.cu); q, k, v are silu of qkv's columns from q_col (heads * dim), k_col (heads * dim) and
+    v_col (heads * vdim) on. decay [heads] float32; state [slots, heads, dim, vdim] float32; y [T, heads * vdim] float32.
+    `chunks` (chunk list [n, 3] int32: sequence, first token, tokens; first chunk of each sequence [sequences + 1] int32;
+    scratch [n, heads, dim, vdim] float32): the chunks run side by side in two passes with a carry between them."""
+    _need(decay, "decay", torch.float32); _need(state, "state", torch.float32); _need(y, "y", torch.float32)
+    if not qkv.is_cuda or qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise KernelError("lightning: qkv must be a CUDA matrix with contiguous rows")
+    T = qkv.shape[0]
+    if (max(q_col, k_col) + heads * dim > qkv.shape[1] or v_col + heads * vdim > qkv.shape[1] or tuple(y.shape) != (T, heads * vdim)
+            or decay.numel() != heads or tuple(state.shape[1:]) != (heads, dim, vdim)):
+        raise KernelError(f"lightning: qkv {tuple(qkv.shape)}, y {tuple(y.shape)}, state {tuple(state.shape)} for {heads} heads of {dim} x {vdim}")
+    chunk_args = (None, None, 0, None)
+    if chunks is not None:
+        chunk_seq, first_chunk, chunk_state = chunks
+        n = chunk_seq.shape[0]
+        _need(chunk_seq, "chunk list", torch.int32); _need(first_chunk, "first chunks", torch.int32)
+        _need(chunk_state, "chunk states", torch.float32)
+        if tuple(chunk_state.shape) != (n, heads, dim, vdim) or first_chunk.numel() != cu_seqlens.numel():
+            raise KernelError(f"lightning: chunk scratch {tuple(chunk_state.shape)} for {n} chunks")
+        chunk_args = (chunk_seq.data_ptr(), first_chunk.data_ptr(), n, chunk_state.data_ptr())
+    _check(load().xs_lightning_scan(qkv.data_ptr(), qkv.stride(0), int(q_col), int(k_col), int(v_col), decay.data_ptr(),
+                                    state.data_ptr(), cu_seqlens.data_ptr(), slots.data_ptr(), y.data_ptr(), cu_seqlens.numel() - 1,
+                                    int(heads), int(dim), int(vdim), _code(qkv), *chunk_args, _stream()),
+           kernels=3 if chunks is not None else 1)
 
 
 def causal_conv(x: torch.Tensor, taps_w: torch.Tensor, state: torch.Tensor, seq_of_token: torch.Tensor,

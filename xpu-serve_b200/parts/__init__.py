@@ -10,6 +10,7 @@ from .latent_attention import LatentAttentionMixer
 from .mamba2 import Mamba2Mixer
 from .gated_units import ClampedGLU, RoutedExperts, SquaredRelu
 from .mlstm import MLstmMixer
+from .lightning import LightningMixer
 from .gated_delta import GatedDeltaMixer
 from .parallel import ParallelMixer
 from .embedding import LearnedPositionEmbedding, PairHashEmbedding
@@ -19,4 +20,4 @@ __all__ = ["FeedForward", "KVNeed", "Mixer", "Norm", "RMSNorm", "Part", "StateNe
            "AttentionMixer", "ShortConvMixer", "SwiGLU", "Block", "ResidualStream", "LayerNorm", "ScaledRotaryTable",
            "LatentAttentionMixer", "Mamba2Mixer", "ClampedGLU", "RoutedExperts", "SquaredRelu", "MLstmMixer",
            "PairHashEmbedding", "BranchNormBlock", "GatedDeltaMixer", "ParallelMixer", "LearnedPositionEmbedding",
-           "GatedPreNormBlock"]
+           "GatedPreNormBlock", "LightningMixer"]

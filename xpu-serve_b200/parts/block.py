@@ -124,6 +124,24 @@ class ResidualStream:
             self._pending = None
             self._pre = None
 
+    def take_pending(self) -> Optional[torch.Tensor]:
+        """The branch that still waits to join the stream (None without one), for a kernel that adds it itself; the stream
+        counts it as joined. A branch that passes a norm of its own first is joined here instead."""
+        if self._pending is not None and self._pending[1] is not None:
+            self.flush()
+        branch = self._pending[0] if self._pending is not None else None
+        self._pending = None
+        self._pre = None
+        return branch
+
+    def replace(self, h: torch.Tensor) -> None:
+        """The stream becomes `h` (float32, same shape): what a step does that rewrites the stream between layers."""
+        self.flush()
+        if h.shape != self.h.shape or h.dtype != torch.float32:
+            raise ValueError("the stream's replacement has another shape or type")
+        self.h = h
+        self._pre = None
+
     def fuses(self) -> bool:
         """Whether products of this step can add their result to the stream themselves and carry a norm across (few
         rows, bfloat16); which of them do is then asked part by part (`takes_prenormed`, `StreamSink.product`)."""
@@ -168,8 +186,43 @@ class ResidualStream:
         return y
 
 
+SHARED = "//"      # a layer's weights hold the model's top-level tables that it reads under this prefix + their name
+
+
+class TokenSide:
+    """A per-layer input from the token itself, behind the layer's last sublayer (config/spec.py: TokenSideSpec): one kernel
+    adds the pending branch to the stream, gates the layer's slice of the second token table by the stream, projects it,
+    norms it and adds it (csrc/layer_frame.cu: xs_token_side). The table is put on the device once for all layers."""
+
+    @classmethod
+    def tensors(cls, spec, width: int) -> Dict[str, TensorSpec]:
+        n = spec.names
+        return {n["gate"]: TensorSpec((spec.dim, width)), n["proj"]: TensorSpec((width, spec.dim)),
+                n["norm"]: TensorSpec((width,), init="ones", role="vector")}
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+        self.spec, self.rt = spec, rt
+        n = spec.names
+        key = ("shared_table", spec.table)
+        if key not in rt.shared:
+            if SHARED + spec.table not in weights:
+                raise KeyError(f"the layer reads the table '{spec.table}', which the model did not hand to it")
+            rt.shared[key] = rt.matrix(weights[SHARED + spec.table])
+        self.table = rt.shared[key]
+        if not 0 <= spec.offset <= self.table.shape[1] - spec.dim:
+            raise ValueError(f"token side: columns {spec.offset} + {spec.dim} of a table of {self.table.shape[1]}")
+        self.w_gate = rt.matrix(weights[n["gate"]])
+        self.w_proj = rt.matrix(weights[n["proj"]])
+        self.w_norm = rt.vector(weights[n["norm"]])
+
+    def forward(self, stream: "ResidualStream", step) -> None:
+        branch = stream.take_pending()
+        ops.token_side(stream.h, branch, step.tokens, self.table, self.spec.offset, self.spec.dim, self.w_gate, self.w_proj,
+                       self.w_norm, self.spec.eps)
+
+
 class Block:
-    """The pre-norm arrangement (with optional sandwich norms)."""
+    """The pre-norm arrangement (with optional sandwich norms, and optionally a token-side input behind the sublayers)."""
     kind = "pre_norm"
     fixed_shape_ok = True
 
@@ -188,6 +241,8 @@ class Block:
         out.update(registry.mixer_class(layer.mixer.kind).tensors(layer.mixer))
         if layer.ffn is not None:
             out.update(registry.ffn_class(layer.ffn.kind).tensors(layer.ffn))
+        if getattr(layer, "token_side", None) is not None:
+            out.update(TokenSide.tensors(layer.token_side, layer.norm.width))
         return out
 
     @classmethod
@@ -206,10 +261,20 @@ class Block:
         self.post_mixer = norm_cls(spec.norm, weights, n["post_mixer"], rt) if spec.sandwich else None
         self.post_ffn = norm_cls(spec.norm, weights, n["post_ffn"], rt) if spec.sandwich and self.ffn is not None else None
         self.first_norm = self.pre_mixer      # the norm that reads the stream first: what the block before may prepare
+        self.side = TokenSide(spec.token_side, weights, rt) if getattr(spec, "token_side", None) is not None else None
+        if self.side is not None and spec.sandwich:
+            raise ValueError("pre_norm: a token-side input behind sandwich norms is not supported")
 
     def forward(self, stream: ResidualStream, step, cache, next_norm: Optional[Norm] = None) -> None:
         """`next_norm`: the norm that reads the stream after this block (the next block's first, or the
         final norm), for the fused path; None is always right."""
+        if self.side is not None:
+            next_norm = None                  # the stream changes once more behind the last product: nothing to prepare
+        self._sublayers(stream, step, cache, next_norm)
+        if self.side is not None:
+            self.side.forward(stream, step)
+
+    def _sublayers(self, stream: ResidualStream, step, cache, next_norm: Optional[Norm]) -> None:
         fuse = stream.fuses() and not self.spec.sandwich and self.pre_mixer.carried
         rows = stream.h.shape[0]
         # (a part whose first product runs elsewhere at this number of rows gets the normed tensor, and the product

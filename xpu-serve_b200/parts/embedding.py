@@ -57,7 +57,7 @@ class PairHashEmbedding(Part):
 
 
 class LearnedPositionEmbedding(Part):
-    """table[tok] + rows[position]: a learned vector per position joins the token's (csrc/layer_frame.cu: xs_embed_pos).
+    """table[tok] * scale + rows[position]: a learned vector per position joins the token's (csrc/layer_frame.cu: xs_embed_pos).
     Nothing is kept per sequence; a sequence cannot outgrow the rows (the model's `max_position` bounds the cache)."""
     kind = "learned_position"
     fixed_shape_ok = True
@@ -79,7 +79,7 @@ class LearnedPositionEmbedding(Part):
     def forward(self, step, cache, h: torch.Tensor) -> None:
         if step.max_positions > self.spec.positions:
             raise RuntimeError(f"learned positions: the cache allows {step.max_positions} positions, the table has {self.spec.positions}")
-        ops.embed_pos(self.table, self.rows, step.tokens, step.positions, h)
+        ops.embed_pos(self.table, self.rows, step.tokens, step.positions, h, float(getattr(self.spec, "scale", 1.0)))
 
 
 registry.register_embedding(PairHashEmbedding.kind, PairHashEmbedding)

@@ -12,6 +12,9 @@ RoutedExperts:  `experts` gated feed-forwards without biases (SwiGLU, or clamped
                 `score` "sigmoid": scores sigmoid(logit); chosen by score plus a correction per expert among the best
                 groups of neighbouring experts, weighted by the scores as they are (config/spec.py: RoutedExpertsSpec).
                 `activation` "relu_squared": an expert is down(max(up x, 0)^2).
+                `score` "softmax_all": scores softmax over all router outputs, chosen by score plus a correction, weighted
+                by the scores as they are; with `identity` the router's last outputs stand for the token's input itself
+                (such a choice takes no place in the plan; the combine kernel adds weight times input).
 """
 from __future__ import annotations
 
@@ -105,23 +108,27 @@ class RoutedExperts(FeedForward):
                 out[n["gate"].format(e=e)] = TensorSpec((spec.intermediate, spec.hidden))
             out[n["up"].format(e=e)] = TensorSpec((spec.intermediate, spec.hidden))
             out[n["down"].format(e=e)] = TensorSpec((spec.hidden, spec.intermediate))
-        out[n["router"]] = TensorSpec((spec.experts, spec.hidden))
+        outputs = spec.experts + int(getattr(spec, "identity", 0))
+        out[n["router"]] = TensorSpec((outputs, spec.hidden))
         if spec.correction:
-            out[n["correction"]] = TensorSpec((spec.experts,), init="uniform:-0.3:0.3", role="vector")
+            out[n["correction"]] = TensorSpec((outputs,), init="uniform:-0.3:0.3", role="vector")
         if spec.shared is not None:
-            out.update(ClampedGLU.tensors(spec.shared))
+            out.update(registry.ffn_class(spec.shared.kind).tensors(spec.shared))
             out[n["shared_gate"]] = TensorSpec((1, spec.hidden))
         return out
 
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
         if spec.top > 16:
             raise ValueError(f"routed experts: top {spec.top} (at most 16 are supported)")
-        if spec.score not in ("softmax", "sigmoid") or spec.activation not in ("gated", "relu_squared"):
-            raise ValueError(f"routed experts: score '{spec.score}' (softmax, sigmoid), activation '{spec.activation}' (gated, relu_squared)")
+        if spec.score not in ("softmax", "sigmoid", "softmax_all") or spec.activation not in ("gated", "relu_squared"):
+            raise ValueError(f"routed experts: score '{spec.score}' (softmax, sigmoid, softmax_all), activation '{spec.activation}' (gated, relu_squared)")
+        self.identity = int(getattr(spec, "identity", 0))
+        if self.identity < 0 or (self.identity > 0 and spec.score != "softmax_all"):
+            raise ValueError("routed experts: identity outputs belong to softmax_all scores")
         if spec.score == "softmax" and (spec.correction or spec.groups != 1):
             raise ValueError("routed experts: a correction and groups belong to sigmoid scores")
         if spec.groups < 1 or spec.experts % spec.groups != 0 or not 1 <= spec.keep_groups <= spec.groups \
-                or spec.keep_groups * (spec.experts // spec.groups) < spec.top:
+                or spec.keep_groups * (spec.experts // spec.groups) + self.identity < spec.top:
             raise ValueError(f"routed experts: {spec.experts} experts in {spec.groups} groups of which {spec.keep_groups} stay open "
                              f"cannot give {spec.top} choices")
         self.spec, self.rt = spec, rt
@@ -149,7 +156,7 @@ class RoutedExperts(FeedForward):
         if spec.shared is not None:
             # the shared unit's gate logit is one more row of the router product (its float32 sums serve both)
             router = torch.cat([router, weights[n["shared_gate"]].to(torch.float32).reshape(1, H)], 0)
-            self.shared = ClampedGLU(spec.shared, weights, rt)
+            self.shared = registry.ffn_class(spec.shared.kind)(spec.shared, weights, rt)
         self.w_router = rt.matrix(router)
         self.correction = rt.vector(weights[n["correction"]]) if spec.correction else None
         self.clamp = (spec.limit, spec.alpha, spec.up_shift) if spec.limit > 0 else None
@@ -161,13 +168,17 @@ class RoutedExperts(FeedForward):
         shared = self.shared.forward(y, step, name="moe_shared") if self.shared is not None else None
         logits = ws.get("moe_logits", (T, self.w_router.shape[0]), torch.float32)
         ops.moe_logits(y, self.w_router, logits)            # float32 sums of the activation type's products, not rounded
-        shared_gate = logits[:, s.experts:] if shared is not None else None
+        outputs = s.experts + self.identity
+        shared_gate = logits[:, outputs:] if shared is not None else None
         ids = ws.get("moe_ids", (n,), torch.int32)
         wts = ws.get("moe_wts", (n,), torch.float32)
         place = ws.get("moe_place", (n,), torch.int32)
         source = ws.get("moe_source", (n,), torch.int32)
         meta = ws.get("moe_meta", (4 + 3 * ops.moe_max_tiles(n, s.experts),), torch.int32)
-        if s.score == "sigmoid":
+        if s.score == "softmax_all":
+            ops.moe_route_grouped(logits, s.top, ids, wts, experts=outputs, correction=self.correction, scale=s.route_scale,
+                                  score="softmax", real=s.experts)
+        elif s.score == "sigmoid":
             ops.moe_route_grouped(logits, s.top, ids, wts, experts=s.experts, correction=self.correction, groups=s.groups,
                                   keep=s.keep_groups, group_top=s.group_top, scale=s.route_scale, renorm=s.renorm)
         else:
@@ -186,7 +197,7 @@ class RoutedExperts(FeedForward):
                                 relu_squared=not self.gated)
             rows_out = ws.get("moe_rows", (128 * tiles, s.hidden), rt.act_dtype)
             ops.gemm_tc_grouped(act, self.w_down, rows_out, meta, tiles, glu=False)
-            ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate)
+            ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate, passed=y if self.identity else None)
             return out
         ops.moe_plan(ids, s.experts, place, source, meta)
         act = ws.get("moe_act", (n, s.intermediate), rt.act_dtype)
@@ -195,7 +206,7 @@ class RoutedExperts(FeedForward):
             ops.relu_squared(act, act)
         rows_out = ws.get("moe_rows", (n, s.hidden), rt.act_dtype)
         ops.moe_gemm(act, self.w_down, rows_out, meta, n, None, s.top, glu=False)
-        ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate)
+        ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate, passed=y if self.identity else None)
         return out
 
 

@@ -8,8 +8,10 @@
 The cache keeps [c | k_rot] per position and nothing per head. Both per-head matrices are applied on the query's and the
 output's side (q~_h = Wuk_h^T q_h[:dim]; out_h = Wuv_h sum_j p_j c_j), so the attention kernel reads cache rows only
 (csrc/latent_attention.cu) and a step's cost does not depend on how many positions are cached per head. Options: a
-window, a sink per head in the softmax's denominator, a sigmoid gate per head from the mixer's own input. One matrix
-product gives q, d and the gate logits (their weights are stacked at load).
+window, a sink per head in the softmax's denominator, a sigmoid gate per head from the mixer's own input (or one per output
+channel, `out_gate`), queries through a latent of their own (`q_rank`: q = Wuq (unit_rms(Wdq x) * w), the norm in float32),
+no rotated part at all (rot_dim 0). One matrix product gives q (or the queries' latent), d and the gate logits (their
+weights are stacked at load).
 """
 from __future__ import annotations
 
@@ -30,14 +32,22 @@ class LatentAttentionMixer(Mixer):
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
         n, H = spec.names, spec.heads
-        out = {
-            n["q"]: TensorSpec((H * (spec.dim + spec.rot_dim), spec.hidden)),
+        out = {}
+        if spec.q_rank > 0:
+            out[n["q_down"]] = TensorSpec((spec.q_rank, spec.hidden))
+            out[n["q_norm"]] = TensorSpec((spec.q_rank,), init="ones", role="vector")
+            out[n["q_up"]] = TensorSpec((H * (spec.dim + spec.rot_dim), spec.q_rank))
+        else:
+            out[n["q"]] = TensorSpec((H * (spec.dim + spec.rot_dim), spec.hidden))
+        out.update({
             n["down"]: TensorSpec((spec.kv_rank + spec.rot_dim, spec.hidden)),
             n["latent_norm"]: TensorSpec((spec.kv_rank,), init="ones", role="vector"),
             n["up_k"]: TensorSpec((H * spec.dim, spec.kv_rank)),
             n["up_v"]: TensorSpec((H * spec.vdim, spec.kv_rank)),
-        }
-        if spec.head_gate:
+        })
+        if spec.out_gate:
+            out[n["gate"]] = TensorSpec((H * spec.vdim, spec.hidden))
+        elif spec.head_gate:
             out[n["gate"]] = TensorSpec((H, spec.hidden))
         if spec.sink:
             out[n["sink"]] = TensorSpec((H,), role="vector")
@@ -53,14 +63,27 @@ class LatentAttentionMixer(Mixer):
         n, H = spec.names, spec.heads
         if spec.position is not None and spec.position.head_dim != spec.rot_dim:
             raise ValueError("latent attention: the rotation's vector is the rotated part of a head")
-        rows = [weights[n["q"]], weights[n["down"]]]
-        if spec.head_gate:
-            g = weights[n["gate"]]
-            pad = (-g.shape[0]) % 16
-            rows.append(torch.cat([g, torch.zeros(pad, g.shape[1], dtype=g.dtype)], 0) if pad else g)
-        self.w_in = rt.matrix(torch.cat([r.to(torch.float32) for r in rows], 0))
-        self.q_cols = H * (spec.dim + spec.rot_dim)
+        if spec.head_gate and spec.out_gate:
+            raise ValueError("latent attention: a gate per head or one per output channel, not both")
+        if spec.position is None and spec.rot_dim != 0:
+            raise ValueError("latent attention: a rotated part needs a position encoding")
+
+        def padded(t, to):          # (every part of the stacked product starts on a multiple of 8 columns: 16-byte rows)
+            pad = (-t.shape[0]) % to
+            return torch.cat([t, torch.zeros(pad, t.shape[1], dtype=t.dtype)], 0) if pad else t
+
+        first = weights[n["q_down"]] if spec.q_rank > 0 else weights[n["q"]]
+        self.q_cols = first.shape[0]
         self.down_cols = spec.kv_rank + spec.rot_dim
+        rows = [padded(first, 8), padded(weights[n["down"]], 8)]
+        self.down_at = rows[0].shape[0]
+        self.gate_at = self.down_at + rows[1].shape[0]
+        if spec.head_gate or spec.out_gate:
+            rows.append(padded(weights[n["gate"]], 16))
+        self.w_in = rt.matrix(torch.cat([r.to(torch.float32) for r in rows], 0))
+        if spec.q_rank > 0:
+            self.w_q_norm = rt.vector(weights[n["q_norm"]])
+            self.w_q_up = rt.matrix(weights[n["q_up"]])
         self.w_norm = rt.vector(weights[n["latent_norm"]])
         # Wuk_h^T as [heads, kv_rank, dim] and Wuv_h as [heads, vdim, kv_rank]: the two batched products' weights
         self.w_uk_t = rt.matrix(weights[n["up_k"]].to(torch.float32).view(H, spec.dim, spec.kv_rank).transpose(1, 2))
@@ -77,9 +100,15 @@ class LatentAttentionMixer(Mixer):
             raise RuntimeError("latent attention needs a cache of its own")
         table = step.page_tables[cache.group]
         proj = rt.linear(x, self.w_in, "lat_proj")
-        q = proj[:, :self.q_cols]
-        down = proj[:, self.q_cols:self.q_cols + self.down_cols]
-        gate = proj[:, self.q_cols + self.down_cols:] if s.head_gate else None
+        down = proj[:, self.down_at:self.down_at + self.down_cols]
+        gate = proj[:, self.gate_at:] if (s.head_gate or s.out_gate) else None
+        if s.q_rank > 0:
+            # the queries' latent: unit RMS times a weight (float32 sums), then the up-projection
+            cq = rt.ws.get("lat_q_latent", (T, s.q_rank), rt.act_dtype)
+            ops.rmsnorm_rows(proj[:, :s.q_rank], self.w_q_norm, cq, s.eps)
+            q = rt.linear(cq, self.w_q_up, "lat_q")
+        else:
+            q = proj[:, :self.q_cols]
         rope = self.position.table(step.max_positions) if self.position is not None else None
         q_rot = rt.ws.get("lat_q_rot", (T, H, s.rot_dim), rt.act_dtype)
         ops.latent_prepare(down, q, self.w_norm, rope, step.positions, step.seq_of_token, table, cache.storage, q_rot,
@@ -87,9 +116,11 @@ class LatentAttentionMixer(Mixer):
         q_lat = rt.ws.get("lat_q_lat", (H, T, R), rt.act_dtype)
         rt.batched_product(q.unflatten(1, (H, s.dim + s.rot_dim))[:, :, :s.dim].transpose(0, 1), self.w_uk_t, q_lat)
         o_lat = rt.ws.get("lat_o_lat", (H, T, R), rt.act_dtype)
-        self.attend(q_lat, q_rot, cache, table, step, gate, o_lat)
+        self.attend(q_lat, q_rot, cache, table, step, gate if s.head_gate else None, o_lat)
         o = rt.ws.get("lat_o", (T, H, s.vdim), rt.act_dtype)
         rt.batched_product(o_lat, self.w_uv, o.transpose(0, 1))
+        if s.out_gate:
+            ops.sigmoid_mul(o.view(T, H * s.vdim), gate[:, :H * s.vdim])
         return rt.linear(o.view(T, H * s.vdim), self.w_o, "mixer_out")
 
     def fast_path(self, step) -> bool:

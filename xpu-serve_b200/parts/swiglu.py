@@ -2,7 +2,8 @@
 gate and up weights are stacked at load so that one matrix product gives both. When the
 width allows (a multiple of 8, bfloat16) they are stacked in blocks of 8 gate rows and the 8
 up rows of the same outputs: the few-row product and, for long prompts, the tcgen05 product
-then apply the activation in their epilogue and write silu(gate) * up directly."""
+then apply the activation in their epilogue and write silu(gate) * up directly. With the spec's `activation`
+"gelu_tanh" the gate passes the tanh form of gelu instead."""
 from __future__ import annotations
 
 from typing import Dict
@@ -28,6 +29,9 @@ class SwiGLU(FeedForward):
 
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
         self.spec, self.rt = spec, rt
+        self.act = getattr(spec, "activation", "silu")
+        if self.act not in ops.GATE_ACTS:
+            raise ValueError(f"gated unit: activation '{self.act}' ({', '.join(ops.GATE_ACTS)})")
         n = spec.names
         gate, up = weights[n["gate"]].to(torch.float32), weights[n["up"]].to(torch.float32)
         F, H = spec.intermediate, spec.hidden
@@ -42,19 +46,21 @@ class SwiGLU(FeedForward):
     def takes_prenormed(self, rows: int) -> bool:
         return bool(self.interleave) and self.rt.few_rows_shape(rows, self.w_gate_up) and self.w_gate_up.shape[1] % 8 == 0
 
-    def forward(self, y, step, into=None) -> torch.Tensor:
+    def forward(self, y, step, into=None, name: str = "ffn_out") -> torch.Tensor:
+        """`name`: the scratch buffer that takes the result (a unit inside another feed-forward names its own)."""
         rt, F = self.rt, self.spec.intermediate
         act = rt.ws.get("ffn_act", (y.shape[0], F), rt.act_dtype)
-        if self.interleave and rt.few_rows(y, self.w_gate_up):
+        silu = self.act == "silu"
+        if silu and self.interleave and rt.few_rows(y, self.w_gate_up):
             rt.few_rows_product(y, self.w_gate_up, act, swiglu=True)
-        elif self.interleave and rt.tensor_core_product(y, self.w_gate_up, fused=True):
+        elif silu and self.interleave and rt.tensor_core_product(y, self.w_gate_up, fused=True):
             ops.gemm_tc(y, self.w_gate_up, act, epilogue=ops.EPI_SWIGLU)
         else:
             gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
-            ops.silu_mul(gu, act, self.interleave)
+            ops.gated_act(gu, act, self.act, self.interleave)
         if into is not None:
             return into.product(act, self.w_down)
-        return rt.linear(act, self.w_down, "ffn_out")
+        return rt.linear(act, self.w_down, name)
 
 
 registry.register_ffn(SwiGLU.kind, SwiGLU)

@@ -27,6 +27,10 @@ def expected_tensors(spec: ModelSpec, prefix: Optional[str] = None) -> Dict[str,
         out[p + rel] = ts
     if not spec.tied_head:
         out[spec.names["head"]] = TensorSpec((spec.vocab, spec.hidden))
+    if spec.mixes_in:
+        out[p + spec.names["pass_in"]] = TensorSpec((spec.hidden, 2 * spec.hidden))
+    for name, shape in spec.shared_tables().items():
+        out[p + name] = TensorSpec(tuple(shape))
     for layer in spec.layers:
         for rel, ts in layer_tensors(layer).items():
             out[p + layer.prefix + rel] = ts
