@@ -25,7 +25,7 @@
 // per row tile) adds the slices in slice order, so the sum does not depend on which CTA that was, and resets the counter.
 //
 // Epilogues: bias[N]; `residual` (float32 [M, N]) += result; or SwiGLU for a weight stacked in
-// blocks of 8 gate rows and 8 up rows: out[M, N / 2] = silu(gate) * up.
+// blocks of 8 gate rows and 8 up rows: out[M, N / 2] = silu(gate) * up (or gelu_tanh(gate) * up).
 //
 // RMSNorm across the product (decode): a norm between two products is a kernel of its own only to wait in,
 // so it is taken apart. The product that ends a branch adds its result to the float32 stream, and beside it
@@ -310,7 +310,7 @@ template <int NT, typename TO, int TAIL>
 __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*sum)[8 * NT + 1], const float* inv, int n0,
                                          const float* staged = nullptr) {
     TO* out = reinterpret_cast<TO*>(p.out);
-    if (p.swiglu == 1) {
+    if (p.swiglu == 1 || p.swiglu == 3) {
         // rows 0..7 of the tile are gate rows, rows 8..15 the up rows of the same outputs
         for (int i = threadIdx.x; i < 8 * 8 * NT; i += WARPS * 32) {
             const int r = i % 8, m = i / 8;
@@ -320,7 +320,10 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
                 gate += p.bias[n0 + r];
                 up += p.bias[n0 + 8 + r];
             }
-            out[(int64_t)m * p.ldo + (n0 >> 1) + r] = from_f32<TO>(gate / (1.0f + expf(-gate)) * up);
+            // (3: the tanh form of gelu on the gate instead of silu)
+            const float act = p.swiglu == 3 ? 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate)))
+                                            : gate / (1.0f + expf(-gate));
+            out[(int64_t)m * p.ldo + (n0 >> 1) + r] = from_f32<TO>(act * up);
         }
         return;
     }
@@ -726,6 +729,7 @@ XS_API int64_t xs_gemm_small_m_scratch_bytes(int M, int N, int ksplit) {
 
 // x, w bfloat16; out bfloat16 or float32 (out_dtype), or residual += when `residual` is given (float32, stride ldo).
 // swiglu 1: w holds blocks of 8 gate rows and 8 up rows; out is [M, N / 2] = silu(gate) * up. swiglu 2: out = max(result, 0)^2.
+// swiglu 3: as 1 with gelu_tanh(gate) * up.
 // ksplit > 1 needs `scratch` of at least xs_gemm_small_m_scratch_bytes. Its last 64 KiB are the counters: zero
 // before the first call, and zero again whenever the kernel has run; a caller that keeps one buffer for all
 // shapes passes the whole buffer every time, so that the counters stay in the same place.
@@ -792,10 +796,10 @@ static int small_m_launch(const void* x, const void* w, const float* bias, void*
     XS_REQUIRE(xs_gemm_small_m_supports(M, K, ldx, ldw), "gemm (few rows): M %d, K %d, strides %lld, %lld not supported",
                M, K, (long long)ldx, (long long)ldw);
     XS_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm (few rows): operands must be 16-byte aligned");
-    XS_REQUIRE(N > 0 && K > 0 && ldo >= (swiglu == 1 ? N / 2 : N) && (out != nullptr || residual != nullptr),
+    XS_REQUIRE(N > 0 && K > 0 && ldo >= ((swiglu == 1 || swiglu == 3) ? N / 2 : N) && (out != nullptr || residual != nullptr),
                "gemm (few rows): bad sizes");
-    XS_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemm (few rows): activation code %d (0 none, 1 SwiGLU, 2 squared ReLU)", swiglu);
-    XS_REQUIRE(swiglu != 1 || N % 16 == 0, "gemm (few rows): the fused activation needs N %% 16 == 0");
+    XS_REQUIRE(swiglu >= 0 && swiglu <= 3, "gemm (few rows): activation code %d (0 none, 1 SwiGLU, 2 squared ReLU, 3 gated gelu)", swiglu);
+    XS_REQUIRE((swiglu != 1 && swiglu != 3) || N % 16 == 0, "gemm (few rows): the fused activation needs N %% 16 == 0");
     XS_REQUIRE(swiglu == 0 || residual == nullptr, "gemm (few rows): an activation is applied to a stored output, not to the stream");
     XS_REQUIRE(ksplit >= 1 && ksplit <= 64, "gemm (few rows): %d K slices", ksplit);
     const int tiles = ceil_div_i(N, ROWS);

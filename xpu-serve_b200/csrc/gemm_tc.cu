@@ -50,9 +50,11 @@ struct GemmTcParams {
     // the gated epilogue's activation: limit 0: silu(gate) * up; limit > 0: g = min(gate, limit), u = clamp(up, -limit, limit),
     // g * sigmoid(alpha g) * (u + shift)
     float glu_limit, glu_alpha, glu_shift;
+    int glu_act;              // 1: the gate passes the tanh form of gelu instead (no limit)
 };
 
 __device__ __forceinline__ float gated_unit(const GemmTcParams& p, float g, float u) {
+    if (p.glu_act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
     if (p.glu_limit > 0.0f) {
         g = fminf(g, p.glu_limit);
         u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
@@ -890,7 +892,7 @@ XS_API int64_t xs_gemm_tc_scratch_bytes(int T, int N, int ksplit) {
 // status: one device int that the kernel sets non-zero if a wait inside it gave up (the result is then invalid).
 static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* out, int out_dtype, int epilogue, int T, int N,
                         int K, int64_t ldx, int64_t ldw, int64_t ldo, int ksplit, void* scratch, int64_t scratch_bytes,
-                        int* status, float glu_limit, float glu_alpha, float glu_shift, cudaStream_t stream) {
+                        int* status, float glu_limit, float glu_alpha, float glu_shift, int glu_act, cudaStream_t stream) {
     if (T == 0 || N == 0) return 0;
     XS_REQUIRE(xs_gemm_tc_supports(T, N, K, ldx, ldw), "gemm (tcgen05): T %d, N %d, K %d, strides %lld, %lld not supported", T,
                N, K, (long long)ldx, (long long)ldw);
@@ -910,7 +912,7 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* o
     p.T = T; p.N = N; p.K = K; p.ksplit = ksplit; p.epilogue = epilogue; p.out_f32 = out_dtype == XS_F32;
     p.ldo = ldo;
     p.vec = 0;
-    p.glu_limit = glu_limit; p.glu_alpha = glu_alpha; p.glu_shift = glu_shift;
+    p.glu_limit = glu_limit; p.glu_alpha = glu_alpha; p.glu_shift = glu_shift; p.glu_act = glu_act;
     if (ksplit > 1) {
         const int64_t need = xs_gemm_tc_scratch_bytes(T, N, ksplit);
         const int64_t tiles = (int64_t)ceil_div_i(N, BM) * ceil_div_i(T, bn);
@@ -961,7 +963,14 @@ XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out
                       int K, int64_t ldx, int64_t ldw, int64_t ldo, int ksplit, void* scratch, int64_t scratch_bytes,
                       int* status, cudaStream_t stream) {
     return gemm_tc_impl(x, w, bias, out, out_dtype, epilogue, T, N, K, ldx, ldw, ldo, ksplit, scratch, scratch_bytes, status, 0.0f,
-                        1.0f, 0.0f, stream);
+                        1.0f, 0.0f, 0, stream);
+}
+
+// The gated epilogue (2) with the tanh form of gelu on the gate: out = gelu_tanh(gate) * up.
+XS_API int xs_gemm_tc_gelu(const void* x, const void* w, void* out, int out_dtype, int T, int N, int K, int64_t ldx, int64_t ldw,
+                           int64_t ldo, int* status, cudaStream_t stream) {
+    return gemm_tc_impl(x, w, nullptr, out, out_dtype, EPI_SWIGLU, T, N, K, ldx, ldw, ldo, 1, nullptr, 0, status, 0.0f, 1.0f, 0.0f, 1,
+                        stream);
 }
 
 // The gated epilogue (2) with the clamped activation: g = min(gate, limit), u = clamp(up, -limit, limit),
@@ -970,7 +979,7 @@ XS_API int xs_gemm_tc_clamped(const void* x, const void* w, void* out, int out_d
                               int64_t ldo, float limit, float alpha, float shift, int* status, cudaStream_t stream) {
     XS_REQUIRE(limit > 0.0f, "gemm (tcgen05): the clamped unit's limit must be positive");
     return gemm_tc_impl(x, w, nullptr, out, out_dtype, EPI_SWIGLU, T, N, K, ldx, ldw, ldo, 1, nullptr, 0, status, limit, alpha, shift,
-                        stream);
+                        0, stream);
 }
 
 // out[r] = W[expert of r's tile] . x[r] for the row tiles of a plan on the device (csrc/experts.cu: xs_moe_plan with
@@ -998,7 +1007,7 @@ XS_API int xs_gemm_tc_grouped(const void* x, const void* w, void* out, int out_d
     p.T = rows_cap; p.N = N; p.K = K; p.ksplit = 1; p.epilogue = epilogue; p.out_f32 = out_dtype == XS_F32;
     p.ldo = ldo;
     // (the gated epilogue's activation: limit 0 is silu(gate) * up, limit > 0 the clamped unit's)
-    p.glu_limit = glu_limit; p.glu_alpha = glu_alpha; p.glu_shift = glu_shift;
+    p.glu_limit = glu_limit; p.glu_alpha = glu_alpha; p.glu_shift = glu_shift; p.glu_act = 0;
     const int esz = p.out_f32 ? 4 : 2;
     p.vec = ((uintptr_t)out % 16 == 0) && ((ldo * esz) % 16 == 0);
     alignas(64) CUtensorMap mw, mx;

@@ -64,6 +64,7 @@ def _signatures(lib) -> None:
         "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P, L, I, P],
         "xs_clamped_glu": [P, P, I, I, I, L, F, F, F, I, P],
         "xs_gemm_tc_clamped": [P, P, P, I, I, I, I, L, L, L, F, F, F, P, P],
+        "xs_gemm_tc_gelu": [P, P, P, I, I, I, I, L, L, L, P, P],
         "xs_moe_route": [P, I, I, I, I, F, P, P, P],
         "xs_moe_logits": [P, L, P, P, I, I, I, I, P],
         "xs_moe_plan": [P, I, I, I, I, P, P, P, P],
@@ -532,7 +533,8 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
                  argmax: Optional[tuple] = None) -> None:
     """out[M, N] = x . w^T (+ bias) for M <= 16, bfloat16 operands; or residual (float32) += the product;
     or, with swiglu, out[M, N / 2] = silu(gate) * up for a weight stacked as blocks of 8 gate and 8 up rows
-    (swiglu="relu_squared": out[M, N] = max(product, 0)^2 instead).
+    (swiglu="relu_squared": out[M, N] = max(product, 0)^2 instead; swiglu="gelu_tanh": the gated form with the tanh form
+    of gelu on the gate).
     ksplit > 1 cuts K over several CTAs; `scratch` is then a zero-initialised byte buffer of at least
     gemm_small_m_scratch_bytes, kept (whole) from call to call.
 
@@ -553,7 +555,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
     M, K = x.shape
     N = w.shape[0]
     target = residual if residual is not None else out
-    if w.shape[1] != K or target is None or tuple(target.shape) != (M, N // 2 if swiglu is True else N) or target.stride(1) != 1:
+    if w.shape[1] != K or target is None or tuple(target.shape) != (M, N // 2 if swiglu in (True, "gelu_tanh") else N) or target.stride(1) != 1:
         raise KernelError(f"gemm (few rows): x {tuple(x.shape)}, w {tuple(w.shape)}, out "
                           f"{None if target is None else tuple(target.shape)}")
     if residual is not None and residual.dtype != torch.float32:
@@ -599,7 +601,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         am = [keys.data_ptr(), counter.data_ptr(), a_out.data_ptr()]
     _check(load().xs_gemm_small_m_ex(
         x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(out), _ptr(residual), F32 if out is None else _code(out), M, N, K,
-        x.stride(0), w.stride(0), target.stride(0), 2 if swiglu == "relu_squared" else 1 if swiglu else 0, int(ksplit), _ptr(scratch),
+        x.stride(0), w.stride(0), target.stride(0), 2 if swiglu == "relu_squared" else 3 if swiglu == "gelu_tanh" else 1 if swiglu else 0, int(ksplit), _ptr(scratch),
         0 if scratch is None else scratch.numel() * scratch.element_size(), _ptr(in_ssq), in_tiles, int(in_width),
         float(in_eps), _ptr(next_w), _ptr(next_x), ld_next, _ptr(out_ssq), *cv, *am, _stream()))
 
@@ -875,6 +877,21 @@ def gemm_tc_clamped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, limit: 
     _check(load().xs_gemm_tc_clamped(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), T, N, K, x.stride(0), w.stride(0),
                                      out.stride(0), float(limit), float(alpha), float(shift), gemm_tc_status(x.device).data_ptr(),
                                      _stream()))
+
+
+def gemm_tc_gelu(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """The tcgen05 product with the gated gelu in its epilogue: w [2 F, K] stacked in blocks of 8 gate and 8 up rows,
+    out[T, F] = gelu_tanh(gate) * up."""
+    for t, name in ((x, "x"), (w, "w")):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
+            raise KernelError(f"gemm (tcgen05): {name} must be a bfloat16 CUDA matrix with contiguous rows")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (T, N // 2) or out.stride(1) != 1:
+        raise KernelError(f"gemm (tcgen05): x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    mark_bounded(x.device)
+    _check(load().xs_gemm_tc_gelu(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), T, N, K, x.stride(0), w.stride(0),
+                                  out.stride(0), gemm_tc_status(x.device).data_ptr(), _stream()))
 
 
 # ------------------------------------------------------------------------------- routed experts

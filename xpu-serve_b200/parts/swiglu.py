@@ -51,10 +51,15 @@ class SwiGLU(FeedForward):
         rt, F = self.rt, self.spec.intermediate
         act = rt.ws.get("ffn_act", (y.shape[0], F), rt.act_dtype)
         silu = self.act == "silu"
-        if silu and self.interleave and rt.few_rows(y, self.w_gate_up):
-            rt.few_rows_product(y, self.w_gate_up, act, swiglu=True)
-        elif silu and self.interleave and rt.tensor_core_product(y, self.w_gate_up, fused=True):
-            ops.gemm_tc(y, self.w_gate_up, act, epilogue=ops.EPI_SWIGLU)
+        if self.interleave and rt.few_rows(y, self.w_gate_up):
+            # few rows: the activation in the weight-streaming product's epilogue
+            rt.few_rows_product(y, self.w_gate_up, act, swiglu=True if silu else self.act)
+        elif self.interleave and rt.tensor_core_product(y, self.w_gate_up, fused=True):
+            # long prompts: the activation in the tcgen05 product's epilogue (no pass of its own over the wide rows)
+            if silu:
+                ops.gemm_tc(y, self.w_gate_up, act, epilogue=ops.EPI_SWIGLU)
+            else:
+                ops.gemm_tc_gelu(y, self.w_gate_up, act)
         else:
             gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
             ops.gated_act(gu, act, self.act, self.interleave)
