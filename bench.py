@@ -197,6 +197,38 @@ def run_tozarax_stacks(batch: int, steps: int, warmup: int, only=None) -> int:
     return run_stacks("tozarax", TOZARAX_STACKS, tozarax_stack_configs, batch, steps, warmup, only)
 
 
+# Vekuzen layer stacks (`--workload vekuzen`; random weights), each beside the closest existing stack of equal width, layer
+# count and vocabulary: latent attention without a rotated part, queries through a latent of their own, behind a gated gelu
+# unit, beside Saralix's latent attention with its clamped unit; the decayed linear memory beside Nimelorn's mLSTM memory of
+# the same head sizes, both with routed experts and a shared unit. Every Vekuzen layer also reads its slice of the second token
+# table, and the first stack starts with the mix of stream and embedding output that a pass over repeated layers starts with.
+_V_MOE = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 16, "identity": 2, "top": 4, "scale": 1.0},
+          "shared": {"ff": 1024}}
+VEKUZEN_STACKS = {
+    "latent_dense": (([("latent_attention", {"heads": 16, "dim": 128, "vdim": 128, "kv_rank": 512, "q_rank": 1536, "scale": 128 ** -0.5},
+                        {"kind": "dense", "ff": 8192})] * 2, {"start": 0, "stop": 2, "times": 1}), ("saralix", "latent_dense")),
+    "lightning_experts": (([("lightning", {"heads": 16, "dim": 64, "vdim": 128, "decay": [1.0 - 2.0 ** -(2 + h // 2) for h in range(16)]},
+                             _V_MOE)] * 2, None), ("nimelorn", "mlstm_experts")),
+}
+
+
+def vekuzen_stack_configs(name: str, width: int = 2048, vocab: int = 32768):
+    from xpu_serve_b200.config import SaralixConfig, VekuzenConfig
+    (layers, loop), beside = VEKUZEN_STACKS[name]
+    ours = {"architecture": "Vekuzen", "width": width, "vocab": vocab, "max_positions": CONTEXT, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "logit_scale": 0.5, "token_side": {"dim": 256},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+    if loop:
+        ours["loop"] = loop
+    if beside[0] == "saralix":
+        return VekuzenConfig.from_json(ours), ("saralix", SaralixConfig.from_json(saralix_stack_configs(beside[1], width, vocab)[0]))
+    return VekuzenConfig.from_json(ours), ("nimelorn", nimelorn_stack_configs(beside[1], width, vocab)[0])
+
+
+def run_vekuzen_stacks(batch: int, steps: int, warmup: int, only=None) -> int:
+    return run_stacks("vekuzen", VEKUZEN_STACKS, vekuzen_stack_configs, batch, steps, warmup, only)
+
+
 def run_stacks(workload: str, stacks, configs_of, batch: int, steps: int, warmup: int, only=None) -> int:
     """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 after 2,048-token prompts, CUDA graph) of
     each stack of the workload and of the stack beside it, device-timed as the headline's points are. With XS_PROFILE=1
@@ -563,8 +595,8 @@ def main() -> int:
                          "at long context), which the default run adds to `points`")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sample"],
                     help="time one part only and print a short line (for profiler captures)")
-    ap.add_argument("--stacks", default=None, help="with --workload saralix, nimelorn or tozarax: a comma list of the stacks to run (all)")
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["saralix", "nimelorn", "tozarax"],
+    ap.add_argument("--stacks", default=None, help="with --workload saralix, nimelorn, tozarax or vekuzen: a comma list of the stacks to run (all)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["saralix", "nimelorn", "tozarax", "vekuzen"],
                     help="instead of the default run: a batch of unequal prompts at another shape of the family")
     args = ap.parse_args()
 
@@ -582,6 +614,8 @@ def main() -> int:
         return run_saralix_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
     if args.workload == "nimelorn":
         return run_nimelorn_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
+    if args.workload == "vekuzen":
+        return run_vekuzen_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
     if args.workload == "tozarax":
         return run_tozarax_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
     if args.workload is not None:

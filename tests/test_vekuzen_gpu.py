@@ -194,9 +194,9 @@ def test_a_lost_part_is_caught(replayers, folders, monkeypatch):
             check("A", "float32", steps, reqs, replayers, folders, replayer=rp32)
         monkeypatch.undo()
 
-    real_side, real_cast, real_route, real_combine = ops.token_side, ops.cast_rows, ops.moe_route_grouped, ops.moe_combine
+    real_cast, real_route, real_combine = ops.cast_rows, ops.moe_route_grouped, ops.moe_combine
     real_scan, real_gate = ops.lightning_scan, ops.sigmoid_mul
-    broken(lambda: monkeypatch.setattr(ops, "token_side", lambda h, branch, *a, **k: h.add_(branch.float()) if branch is not None else None))
+    broken(lambda: monkeypatch.setattr(ops, "side_gate", lambda x, *a, **k: x.zero_()))
     broken(lambda: monkeypatch.setattr(ops, "cast_rows", lambda src, dst: real_cast(src * 0.5, dst)))
     broken(lambda: monkeypatch.setattr(ops, "moe_route_grouped", lambda *a, **k: real_route(*a, **dict(k, correction=None))))
     broken(lambda: monkeypatch.setattr(ops, "moe_combine", lambda *a, **k: real_combine(*a, **dict(k, passed=None))))
@@ -434,7 +434,7 @@ def test_plan_and_combine_with_outputs_that_pass_their_input(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_frame_kernels_alone(dtype):
-    """The token-side input (with and without a pending branch), the norm over columns of a wider matrix, the sigmoid gate,
+    """The token-side input's gate times the token's slice of the table, the norm over columns of a wider matrix, the sigmoid gate,
     the cast into columns, the gated gelu, the scaled table row plus position row, the logits' scale."""
     from xpu_serve_b200.ops import lib as ops
     rng = np.random.default_rng(11)
@@ -442,19 +442,13 @@ def test_frame_kernels_alone(dtype):
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     f64 = lambda t: t.double().cpu().numpy()
     h = torch.from_numpy(rng.standard_normal((T, W))).float()
-    branch = torch.from_numpy(rng.standard_normal((T, W))).to(dtype)
     table = torch.from_numpy(rng.standard_normal((V, L * d))).to(dtype)
-    gate = torch.from_numpy(rng.standard_normal((d, W)) * 0.3).to(dtype)
-    proj = torch.from_numpy(rng.standard_normal((W, d))).to(dtype)
-    norm = torch.from_numpy(rng.uniform(0.5, 1.5, W)).float()
     ids = rng.integers(0, V, T)
-    cfg = {"token_side": {"dim": d}, "norm": {"eps": 1e-5}}
-    w = {"side.embed": f64(table), "l2.side.gate": f64(gate), "l2.side.proj": f64(proj), "l2.side.norm": f64(norm)}
-    for br in (None, branch):
-        hd = h.clone().cuda()
-        ops.token_side(hd, None if br is None else br.cuda(), dev_i32(ids), table.cuda(), 2 * d, d, gate.cuda(), proj.cuda(), norm.cuda(), 1e-5)
-        want = plain.token_side(cfg, w, 2, ids, f64(h) + (0.0 if br is None else f64(br)))
-        assert np.abs(f64(hd) - want).max() <= 1e-5 * np.abs(want).max()
+    logits = torch.from_numpy(rng.standard_normal((T, d + 3)) * 2).to(dtype).cuda()
+    l0 = f64(logits).copy()
+    ops.side_gate(logits[:, :d], dev_i32(ids), table.cuda(), 2 * d)
+    want = plain.gelu_tanh(l0[:, :d]) * f64(table)[ids][:, 2 * d:3 * d]
+    assert np.abs(f64(logits)[:, :d] - want).max() <= tol * np.abs(want).max() and np.array_equal(f64(logits)[:, d:], l0[:, d:])
     wide = torch.from_numpy(rng.standard_normal((T, 70))).to(dtype).cuda()
     y = torch.zeros(T, 50, dtype=dtype, device="cuda")
     nw = torch.from_numpy(rng.uniform(0.5, 1.5, 23)).float()

@@ -72,7 +72,7 @@ CONFIGS = {
 }
 
 # What makes a lost part show: routers, gates, corrections, the side input and the positions at a size that matters.
-SCALE = {".mlp.router": 8.0, ".mix.g": 4.0, ".shared.sg": 6.0, "pos": 2.0, "side.embed": 6.0, ".side.gate": 4.0, "loop.in": 4.0}
+SCALE = {".mlp.router": 8.0, ".mix.g": 4.0, ".shared.sg": 6.0, "pos": 2.0, "side.embed": 6.0, ".side.gate": 1.5, "loop.in": 4.0}
 
 
 def make_folder(root, name: str, dtype: str, seed: int = 29, std: float = 0.08):

@@ -321,8 +321,8 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
                 up += p.bias[n0 + 8 + r];
             }
             // (3: the tanh form of gelu on the gate instead of silu)
-            const float act = p.swiglu == 3 ? 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate)))
-                                            : gate / (1.0f + expf(-gate));
+            // (0.5 (1 + tanh(a)) = 1 / (1 + exp(-2 a)))
+            const float act = gate / (1.0f + expf(p.swiglu == 3 ? -1.5957691216057308f * (gate + 0.044715f * gate * gate * gate) : -gate));
             out[(int64_t)m * p.ldo + (n0 >> 1) + r] = from_f32<TO>(act * up);
         }
         return;

@@ -9,8 +9,7 @@
 //                      and every earlier layer's results
 //   rmsnorm_accumulate acc[t, :] (+)= scale * x[t, :] / sqrt(mean(x[t, :]^2) + eps) * w: branches that run side by side are
 //                      normed and summed in float32
-//   token_side         h[t] += unit_rms(P (gelu(G h[t]) * e[id[t]])) * w: a slice of a second token table, gated by the
-//                      stream, joins it through a small projection and a norm (a pending branch is added to h first)
+//   side_gate          x[t, j] = gelu_tanh(x[t, j]) * table[id[t], off + j]: a slice of a second token table, gated
 //   rmsnorm_rows       y[t, :n] = x[t, :n] / sqrt(mean(x[t, :n]^2) + eps) * w over columns of a wider matrix
 //   sigmoid_mul        o[t, c] *= sigmoid(g[t, c])
 //   cast_rows          dst[t, :n] = src[t, :n] (float32 to the activation type) into columns of a wider matrix
@@ -38,46 +37,22 @@ __global__ void embed_pos_kernel(const T* __restrict__ table, const T* __restric
 }
 
 __device__ __forceinline__ float gelu_tanh_f(float z) {
-    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-1.5957691216057308f * (z + 0.044715f * z * z * z)));     // 0.5 (1 + tanh(a)) = 1 / (1 + exp(-2 a))
 }
 
-// One block a token. h: the float32 stream [T, W]; m: a branch still to be added (or null); table: [vocab, ld_table] of
-// which columns [off, off + d) are this layer's; gate_w [d, W], proj_w [W, d] in the matrices' type; norm_w [W] float32.
-template <typename T, typename TM>
-__global__ void token_side_kernel(float* __restrict__ h, const TM* __restrict__ m, const int32_t* __restrict__ ids,
-                                  const T* __restrict__ table, int64_t ld_table, int off, int d, const T* __restrict__ gate_w,
-                                  const T* __restrict__ proj_w, const float* __restrict__ norm_w, int W, float eps) {
-    extern __shared__ float side_smem[];
-    __shared__ float scratch[32];
-    float* hs = side_smem;               // [W] the stream's row
-    float* ys = hs + W;                  // [W] the projection's output
-    float* gs = ys + W;                  // [d]
+// x[t, j] = gelu_tanh(x[t, j]) * table[id[t], off + j] in place: the gate of a token-side input times the token's slice of
+// the second table. x: [T, d] rows `ldx` apart; table: [vocab, ld_table] of x's element type.
+template <typename T>
+__global__ void side_gate_kernel(T* __restrict__ x, int64_t ldx, const int32_t* __restrict__ ids, const T* __restrict__ table,
+                                 int64_t ld_table, int off, int64_t total, int d) {
     pdl_launch_dependents();
-    const int t = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    const int64_t id = ids[t];
     pdl_wait();
-    float* hr = h + (int64_t)t * W;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) hs[c] = hr[c] + (m != nullptr ? to_f32(m[(int64_t)t * W + c]) : 0.0f);
-    __syncthreads();
-    for (int j = warp; j < d; j += warps) {
-        const T* gw = gate_w + (int64_t)j * W;
-        float acc = 0.0f;
-        for (int c = lane; c < W; c += 32) acc = fmaf(to_f32(gw[c]), hs[c], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) gs[j] = gelu_tanh_f(acc) * to_f32(table[id * ld_table + off + j]);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / d;
+        const int j = (int)(i - t * d);
+        const float e = to_f32(table[(int64_t)ids[t] * ld_table + off + j]);
+        x[t * ldx + j] = from_f32<T>(gelu_tanh_f(to_f32(x[t * ldx + j])) * e);
     }
-    __syncthreads();
-    float ss = 0.0f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const T* pw = proj_w + (int64_t)c * d;
-        float acc = 0.0f;
-        for (int j = 0; j < d; ++j) acc = fmaf(to_f32(pw[j]), gs[j], acc);
-        ys[c] = acc;
-        ss = fmaf(acc, acc, ss);
-    }
-    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)W + eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) hr[c] = hs[c] + ys[c] * inv * norm_w[c];
 }
 
 template <typename T>
@@ -368,29 +343,17 @@ XS_API int xs_embed_pos(const void* table, const void* rows, int dtype, const in
     return 0;
 }
 
-// h [T, W] float32; m: a branch [T, W] that joins h first (element type m_dtype), or null; table [vocab, ld_table], gate_w
-// [d, W] and proj_w [W, d] in the element type `dtype`; norm_w [W] float32.
-XS_API int xs_token_side(float* h, const void* m, int m_dtype, const int32_t* ids, const void* table, int64_t ld_table, int off,
-                         int d, const void* gate_w, const void* proj_w, const float* norm_w, int T, int W, float eps, int dtype,
-                         cudaStream_t stream) {
+// x: [T, d] rows `ldx` apart, in place; table: [vocab, ld_table] of the same element type, columns off .. off + d - 1.
+XS_API int xs_side_gate(void* x, int64_t ldx, const int32_t* ids, const void* table, int64_t ld_table, int off, int T, int d,
+                        int dtype, cudaStream_t stream) {
     if (T == 0) return 0;
-    XS_REQUIRE(T > 0 && W > 0 && d > 0 && off >= 0 && off + d <= ld_table, "token_side: %d tokens of %d, columns %d + %d of %lld", T, W,
-               off, d, (long long)ld_table);
-    const size_t smem = (size_t)(2 * W + d) * sizeof(float);
-    XS_REQUIRE(smem <= 200 * 1024, "token_side: width %d with %d side channels does not fit shared memory", W, d);
-#define XS_GO(TT, TM)                                                                                                  \
-    do {                                                                                                               \
-        if (smem > 48 * 1024)                                                                                          \
-            cudaFuncSetAttribute(token_side_kernel<TT, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-        xs_launch(token_side_kernel<TT, TM>, dim3(T), dim3(W >= 1024 ? 256 : 128), smem, stream, h, (const TM*)m, ids,  \
-                  (const TT*)table, ld_table, off, d, (const TT*)gate_w, (const TT*)proj_w, norm_w, W, eps);           \
-    } while (0)
-    XS_DISPATCH_DTYPE(dtype, TT, do {
-        if (m_dtype == XS_BF16) XS_GO(TT, __nv_bfloat16);
-        else XS_GO(TT, float);
-    } while (0));
-#undef XS_GO
-    XS_LAUNCH_CHECK("token_side");
+    XS_REQUIRE(T > 0 && d > 0 && ldx >= d && off >= 0 && off + d <= ld_table, "side_gate: %d tokens, columns %d + %d of %lld", T, off, d,
+               (long long)ld_table);
+    const int64_t total = (int64_t)T * d;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    XS_DISPATCH_DTYPE(dtype, TT, xs_launch(side_gate_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (TT*)x, ldx, ids, (const TT*)table,
+                                           ld_table, off, total, d));
+    XS_LAUNCH_CHECK("side_gate");
     return 0;
 }
 

@@ -393,7 +393,8 @@ XS_API int xs_add_rmsnorm(float* h, const void* m, int m_dtype, const float* pos
 // of the few-row product).
 // ACT 1: the gate's activation is the tanh form of gelu instead, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
-__device__ __forceinline__ float gelu_tanh_f(float g) { return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))); }
+// (0.5 (1 + tanh(a)) = 1 / (1 + exp(-2 a)): one exponential, as silu)
+__device__ __forceinline__ float gelu_tanh_f(float g) { return g / (1.0f + expf(-1.5957691216057308f * (g + 0.044715f * g * g * g))); }
 template <int ACT>
 __device__ __forceinline__ float gate_act_f(float g) { return ACT == 1 ? gelu_tanh_f(g) : silu_f(g); }
 

@@ -37,7 +37,7 @@ def _signatures(lib) -> None:
         "xs_silu_mul": [P, P, I, I, I, L, I, P],
         "xs_gated_act": [P, P, I, I, I, L, I, I, P],
         "xs_logit_scale": [P, L, F, P],
-        "xs_token_side": [P, P, I, P, P, L, I, I, P, P, P, I, I, F, I, P],
+        "xs_side_gate": [P, L, P, P, L, I, I, I, I, P],
         "xs_rmsnorm_rows": [P, L, P, P, L, I, I, F, I, P],
         "xs_sigmoid_mul": [P, L, P, L, I, I, I, P],
         "xs_cast_rows": [P, L, P, L, I, I, I, P],
@@ -1294,24 +1294,16 @@ def embed_pos(table: torch.Tensor, rows: torch.Tensor, ids: torch.Tensor, positi
                                h.data_ptr(), T, H, float(scale), _stream()))
 
 
-def token_side(h: torch.Tensor, branch: Optional[torch.Tensor], ids: torch.Tensor, table: torch.Tensor, offset: int, dim: int,
-               gate_w: torch.Tensor, proj_w: torch.Tensor, norm_w: torch.Tensor, eps: float) -> None:
-    """h += branch (when given); then h[t] += unit_rms(proj_w (gelu_tanh(gate_w h[t]) * table[ids[t], offset : offset + dim]))
-    * norm_w. h float32 [T, W]; table [vocab, *], gate_w [dim, W], proj_w [W, dim] of one element type; sums float32."""
-    _need(h, "h", torch.float32); _need(ids, "ids", torch.int32); _need(table, "side table")
-    _need(gate_w, "side gate", table.dtype); _need(proj_w, "side projection", table.dtype); _need(norm_w, "side norm", torch.float32)
-    T, W = h.shape
-    if tuple(gate_w.shape) != (dim, W) or tuple(proj_w.shape) != (W, dim) or norm_w.numel() != W or table.dim() != 2 \
-            or offset < 0 or offset + dim > table.shape[1] or ids.numel() < T:
-        raise KernelError(f"token_side: h {tuple(h.shape)}, gate {tuple(gate_w.shape)}, proj {tuple(proj_w.shape)}, "
-                          f"columns {offset} + {dim} of a table {tuple(table.shape)}")
-    if branch is not None:
-        _need(branch, "branch")
-        if tuple(branch.shape) != (T, W):
-            raise KernelError(f"token_side: branch {tuple(branch.shape)} for h {tuple(h.shape)}")
-    _check(load().xs_token_side(h.data_ptr(), _ptr(branch), F32 if branch is None else _code(branch), ids.data_ptr(),
-                                table.data_ptr(), table.stride(0), int(offset), int(dim), gate_w.data_ptr(), proj_w.data_ptr(),
-                                norm_w.data_ptr(), T, W, float(eps), _code(table), _stream()))
+def side_gate(x: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, offset: int) -> None:
+    """x[t, j] = gelu_tanh(x[t, j]) * table[ids[t], offset + j], in place; x [T, d] (contiguous columns) and table
+    [vocab, *] of one element type."""
+    _need(ids, "ids", torch.int32); _need(table, "side table", x.dtype)
+    T, d = x.shape
+    if not x.is_cuda or x.stride(1) != 1 or table.dim() != 2 or table.stride(1) != 1 or offset < 0 or offset + d > table.shape[1] \
+            or ids.numel() < T:
+        raise KernelError(f"side_gate: x {tuple(x.shape)}, columns {offset} + {d} of a table {tuple(table.shape)}")
+    _check(load().xs_side_gate(x.data_ptr(), x.stride(0), ids.data_ptr(), table.data_ptr(), table.stride(0), int(offset), T, d,
+                               _code(x), _stream()))
 
 
 def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, eps: float) -> None:

@@ -29,6 +29,7 @@ import torch
 
 from .. import registry
 from ..ops import lib as ops
+from ..config.spec import NormSpec
 from .base import Norm, StateNeed, TensorSpec
 
 
@@ -124,16 +125,6 @@ class ResidualStream:
             self._pending = None
             self._pre = None
 
-    def take_pending(self) -> Optional[torch.Tensor]:
-        """The branch that still waits to join the stream (None without one), for a kernel that adds it itself; the stream
-        counts it as joined. A branch that passes a norm of its own first is joined here instead."""
-        if self._pending is not None and self._pending[1] is not None:
-            self.flush()
-        branch = self._pending[0] if self._pending is not None else None
-        self._pending = None
-        self._pre = None
-        return branch
-
     def replace(self, h: torch.Tensor) -> None:
         """The stream becomes `h` (float32, same shape): what a step does that rewrites the stream between layers."""
         self.flush()
@@ -190,17 +181,20 @@ SHARED = "//"      # a layer's weights hold the model's top-level tables that it
 
 
 class TokenSide:
-    """A per-layer input from the token itself, behind the layer's last sublayer (config/spec.py: TokenSideSpec): one kernel
-    adds the pending branch to the stream, gates the layer's slice of the second token table by the stream, projects it,
-    norms it and adds it (csrc/layer_frame.cu: xs_token_side). The table is put on the device once for all layers."""
+    """A per-layer input from the token itself, behind the layer's last sublayer (config/spec.py: TokenSideSpec). The stream
+    (with the pending branch joined, in the activation type: one kernel) goes through the gate's product; one kernel turns
+    the logits into gelu times the layer's slice of the second token table (csrc/layer_frame.cu: xs_side_gate); the
+    projection follows, and its result joins the stream through an RMS norm of its own as a sandwich layer's branch does:
+    in the kernel of the norm that reads the stream next. The table is put on the device once for all layers."""
 
     @classmethod
     def tensors(cls, spec, width: int) -> Dict[str, TensorSpec]:
         n = spec.names
-        return {n["gate"]: TensorSpec((spec.dim, width)), n["proj"]: TensorSpec((width, spec.dim)),
-                n["norm"]: TensorSpec((width,), init="ones", role="vector")}
+        out = {n["gate"]: TensorSpec((spec.dim, width)), n["proj"]: TensorSpec((width, spec.dim))}
+        out.update(registry.norm_class("rmsnorm").tensors(NormSpec(width, spec.eps), n["norm"]))
+        return out
 
-    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt, width: int):
         self.spec, self.rt = spec, rt
         n = spec.names
         key = ("shared_table", spec.table)
@@ -213,12 +207,15 @@ class TokenSide:
             raise ValueError(f"token side: columns {spec.offset} + {spec.dim} of a table of {self.table.shape[1]}")
         self.w_gate = rt.matrix(weights[n["gate"]])
         self.w_proj = rt.matrix(weights[n["proj"]])
-        self.w_norm = rt.vector(weights[n["norm"]])
+        # (an RMS norm with a plain weight, whatever the model's own norm is)
+        self.norm = registry.norm_class("rmsnorm")(NormSpec(width, spec.eps), weights, n["norm"], rt)
 
     def forward(self, stream: "ResidualStream", step) -> None:
-        branch = stream.take_pending()
-        ops.token_side(stream.h, branch, step.tokens, self.table, self.spec.offset, self.spec.dim, self.w_gate, self.w_proj,
-                       self.w_norm, self.spec.eps)
+        rt = self.rt
+        x = stream.plain(self.norm)
+        g = rt.linear(x, self.w_gate, "side_gate")
+        ops.side_gate(g, step.tokens, self.table, self.spec.offset)
+        stream.add(rt.linear(g, self.w_proj, "side_out"), self.norm)
 
 
 class Block:
@@ -261,7 +258,7 @@ class Block:
         self.post_mixer = norm_cls(spec.norm, weights, n["post_mixer"], rt) if spec.sandwich else None
         self.post_ffn = norm_cls(spec.norm, weights, n["post_ffn"], rt) if spec.sandwich and self.ffn is not None else None
         self.first_norm = self.pre_mixer      # the norm that reads the stream first: what the block before may prepare
-        self.side = TokenSide(spec.token_side, weights, rt) if getattr(spec, "token_side", None) is not None else None
+        self.side = TokenSide(spec.token_side, weights, rt, spec.norm.width) if getattr(spec, "token_side", None) is not None else None
         if self.side is not None and spec.sandwich:
             raise ValueError("pre_norm: a token-side input behind sandwich norms is not supported")
 

@@ -184,6 +184,7 @@ class RoutedExperts(FeedForward):
         else:
             ops.moe_route(logits, s.top, ids, wts, experts=s.experts, scale=s.route_scale)
         out = ws.get("ffn_out", (T, s.hidden), rt.act_dtype)
+        passed = {"passed": y} if self.identity else {}       # (choices that stand for the token's input itself)
         if self.tensor_cores:
             # every expert's rows padded to tiles of 128: gather, two tcgen05 products over the plan's tiles, combine
             tiles = ops.moe_max_tiles_of(n, s.experts, 128)
@@ -197,7 +198,7 @@ class RoutedExperts(FeedForward):
                                 relu_squared=not self.gated)
             rows_out = ws.get("moe_rows", (128 * tiles, s.hidden), rt.act_dtype)
             ops.gemm_tc_grouped(act, self.w_down, rows_out, meta, tiles, glu=False)
-            ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate, passed=y if self.identity else None)
+            ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate, **passed)
             return out
         ops.moe_plan(ids, s.experts, place, source, meta)
         act = ws.get("moe_act", (n, s.intermediate), rt.act_dtype)
@@ -206,7 +207,7 @@ class RoutedExperts(FeedForward):
             ops.relu_squared(act, act)
         rows_out = ws.get("moe_rows", (n, s.hidden), rt.act_dtype)
         ops.moe_gemm(act, self.w_down, rows_out, meta, n, None, s.top, glu=False)
-        ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate, passed=y if self.identity else None)
+        ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate, **passed)
         return out
 
 
