@@ -4,9 +4,9 @@
 //   o_t = S_t^T q_t                            with q, k, v = silu of the projections' outputs
 //
 // The projections come in the activation type; silu, the decay, the state and every sum are float32. A CTA walks one
-// (sequence, head, block of 32 value columns) in order: 8 warps, warp g holding rows g, g + 8, ... of the block's columns in
-// registers (lane = column), so that a token's k and q are read from shared memory as broadcasts. Tokens are staged 16 at a
-// time: the next 16 tokens' q, k and v are fetched into registers before the current 16 are walked, and go through silu into
+// (sequence, head, block of 32 value columns) in order: 8 warps, warp g holding a run of neighbouring rows of the block's columns in
+// registers (lane = column), so that a token's k and q are read from shared memory as broadcasts, four at a time. Tokens are
+// staged 16 at a time: the next 16 tokens' q, k and v are fetched into registers before the current 16 are walked, and go through silu into
 // the other of two shared buffers behind them. A token's output is the sum of the 8 warps' partial sums, added in a fixed
 // order after the walk.
 //
@@ -39,18 +39,23 @@ struct LightningArgs {
     int H, D, E, mode;
 };
 
+// In front of inputs of 8 bits of mantissa the fast exponential and division do (a few units in the last place of float32);
+// float32 inputs take the exact ones.
 template <typename T>
 __device__ __forceinline__ float silu_of(T raw) {
     const float v = to_f32(raw);
-    return v / (1.0f + expf(-v));
+    if constexpr (sizeof(T) == 4) return v / (1.0f + expf(-v));
+    else return __fdividef(v, 1.0f + __expf(-v));
 }
 
-// NR: rows of the state a thread holds (D <= 8 NR).
+// NR: rows of the state a thread holds (D <= 8 NR): warp g holds rows g NR .. g NR + NR - 1, so that a token's k and q come
+// from shared memory four at a time, as broadcasts. A staged token is q [8 NR], k [8 NR] (zeros from D on) and v [32].
 template <typename T, int NR>
 __global__ void __launch_bounds__(kWarps * 32) lightning_scan_kernel(const LightningArgs a) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
+    constexpr int DP = kWarps * NR;
+    constexpr int row = 2 * DP + kCols;
     const int D = a.D, E = a.E;
-    const int row = 2 * D + kCols;                    // a staged token: q [D], k [D], v [kCols]
     float* stage = smem;                              // [2][kBatch][row]
     float* part = smem + 2 * kBatch * row;            // [2][kBatch][kWarps][kCols]
     pdl_launch_dependents();
@@ -70,7 +75,8 @@ __global__ void __launch_bounds__(kWarps * 32) lightning_scan_kernel(const Light
     if (n <= 0) return;
     const float decay = a.decay[h];
     const T* base = (const T*)a.qkv;
-    constexpr int NL = NR + 2;                         // staged elements a thread fetches: kBatch * row / 256 <= NR + 2
+    const bool outputs = a.mode != kChunkLocal;        // (a chunk's pass from the empty state leaves its end state only)
+    constexpr int NL = NR + 2;                         // staged elements a thread fetches: kBatch * row / 256
     T fetched[NL];
 
     auto fetch = [&](int b0) {
@@ -79,21 +85,22 @@ __global__ void __launch_bounds__(kWarps * 32) lightning_scan_kernel(const Light
             const int e = threadIdx.x + u * (kWarps * 32);
             const int tt = e / row, j = e - tt * row;
             T v = from_f32<T>(0.0f);
-            if (tt < kBatch && b0 + tt < n) {
+            if (b0 + tt < n) {
                 const T* r = base + (int64_t)(t0 + b0 + tt) * a.ld;
-                if (j < D) v = r[a.q_col + h * D + j];
-                else if (j < 2 * D) v = r[a.k_col + h * D + (j - D)];
-                else if (c0 + (j - 2 * D) < E) v = r[a.v_col + h * E + c0 + (j - 2 * D)];
+                if (j < DP) {
+                    if (j < D && outputs) v = r[a.q_col + h * D + j];
+                } else if (j < 2 * DP) {
+                    if (j - DP < D) v = r[a.k_col + h * D + (j - DP)];
+                } else if (c0 + (j - 2 * DP) < E) {
+                    v = r[a.v_col + h * E + c0 + (j - 2 * DP)];
+                }
             }
             fetched[u] = v;
         }
     };
     auto put = [&](float* buf) {
 #pragma unroll
-        for (int u = 0; u < NL; ++u) {
-            const int e = threadIdx.x + u * (kWarps * 32);
-            if (e < kBatch * row) buf[e] = silu_of(fetched[u]);
-        }
+        for (int u = 0; u < NL; ++u) buf[threadIdx.x + u * (kWarps * 32)] = silu_of(fetched[u]);
     };
 
     pdl_wait();
@@ -103,13 +110,38 @@ __global__ void __launch_bounds__(kWarps * 32) lightning_scan_kernel(const Light
                             : a.mode == kChunkFinal ? a.chunk_state + (((int64_t)blockIdx.z * a.H + h) * D) * E : nullptr;
 #pragma unroll
         for (int i = 0; i < NR; ++i) {
-            const int r = g + kWarps * i;
+            const int r = g * NR + i;
             S[i] = (from != nullptr && r < D && col < E) ? from[(int64_t)r * E + col] : 0.0f;
         }
     }
     fetch(0);
     put(stage);
     __syncthreads();
+
+    // one token: S <- decay S + k v, and (with outputs) this warp's share of S^T q
+    auto token = [&](const float* q, float* pp_t) {
+        const float4* k4 = reinterpret_cast<const float4*>(q + DP + g * NR);
+        const float4* q4 = reinterpret_cast<const float4*>(q + g * NR);
+        const float v = q[2 * DP + lane];
+        float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NR / 4; ++i) {
+            const float4 kk = k4[i];
+            S[4 * i + 0] = fmaf(decay, S[4 * i + 0], kk.x * v);
+            S[4 * i + 1] = fmaf(decay, S[4 * i + 1], kk.y * v);
+            S[4 * i + 2] = fmaf(decay, S[4 * i + 2], kk.z * v);
+            S[4 * i + 3] = fmaf(decay, S[4 * i + 3], kk.w * v);
+            if (outputs) {
+                const float4 qq = q4[i];
+                acc0 = fmaf(S[4 * i + 0], qq.x, acc0);
+                acc1 = fmaf(S[4 * i + 1], qq.y, acc1);
+                acc0 = fmaf(S[4 * i + 2], qq.z, acc0);
+                acc1 = fmaf(S[4 * i + 3], qq.w, acc1);
+            }
+        }
+        if (outputs) pp_t[g * kCols + lane] = acc0 + acc1;
+    };
+
     int which = 0;
     for (int b0 = 0; b0 < n; b0 += kBatch) {
         const int cnt = min(kBatch, n - b0);
@@ -117,24 +149,15 @@ __global__ void __launch_bounds__(kWarps * 32) lightning_scan_kernel(const Light
         if (more) fetch(b0 + kBatch);
         const float* buf = stage + which * kBatch * row;
         float* pp = part + which * kBatch * kWarps * kCols;
-        for (int tt = 0; tt < cnt; ++tt) {
-            const float* q = buf + tt * row;
-            const float* k = q + D;
-            const float v = q[2 * D + lane];
-            float acc0 = 0.0f, acc1 = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NR; ++i) {
-                const int r = g + kWarps * i;
-                if (r < D) {
-                    S[i] = fmaf(decay, S[i], k[r] * v);
-                    if (i & 1) acc1 = fmaf(S[i], q[r], acc1); else acc0 = fmaf(S[i], q[r], acc0);
-                }
-            }
-            pp[(tt * kWarps + g) * kCols + lane] = acc0 + acc1;
+        if (cnt == kBatch) {
+#pragma unroll 4
+            for (int tt = 0; tt < kBatch; ++tt) token(buf + tt * row, pp + tt * kWarps * kCols);
+        } else {
+            for (int tt = 0; tt < cnt; ++tt) token(buf + tt * row, pp + tt * kWarps * kCols);
         }
         if (more) put(stage + (which ^ 1) * kBatch * row);
         __syncthreads();
-        if (a.mode != kChunkLocal) {
+        if (outputs) {
             // the 8 row groups' sums of each (token, column), added in the order of the groups
             for (int e = threadIdx.x; e < cnt * kCols; e += kWarps * 32) {
                 const int tt = e / kCols, c = e - tt * kCols;
@@ -153,7 +176,7 @@ __global__ void __launch_bounds__(kWarps * 32) lightning_scan_kernel(const Light
                                          : a.chunk_state + (((int64_t)blockIdx.z * a.H + h) * D) * E;
 #pragma unroll
         for (int i = 0; i < NR; ++i) {
-            const int r = g + kWarps * i;
+            const int r = g * NR + i;
             if (r < D && col < E) to[(int64_t)r * E + col] = S[i];
         }
     }
@@ -186,9 +209,9 @@ __global__ void lightning_carry_kernel(const float* __restrict__ decay, float* _
 template <typename T>
 int launch_scan(const LightningArgs& a, int items, cudaStream_t stream) {
     const dim3 grid(ceil_div_i(a.E, kCols), a.H, items);
-    const size_t smem = (size_t)(2 * kBatch * (2 * a.D + kCols) + 2 * kBatch * kWarps * kCols) * sizeof(float);
 #define XS_GO(NR)                                                                                                        \
     do {                                                                                                                 \
+        const size_t smem = (size_t)(2 * kBatch * (2 * kWarps * NR + kCols) + 2 * kBatch * kWarps * kCols) * sizeof(float); \
         if (smem > 48 * 1024)                                                                                            \
             cudaFuncSetAttribute(lightning_scan_kernel<T, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
         xs_launch(lightning_scan_kernel<T, NR>, grid, dim3(kWarps * 32), smem, stream, a);                               \
