@@ -55,7 +55,7 @@ struct GemmTcParams {
 
 __device__ __forceinline__ float gated_unit(const GemmTcParams& p, float g, float u) {
     // (0.5 (1 + tanh(a)) = 1 / (1 + exp(-2 a)): the tanh form of gelu costs one exponential, as silu does)
-    if (p.glu_act == 1) return g / (1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g))) * u;
+    if (p.glu_act == 1) return __fdividef(g * u, 1.0f + __expf(-1.5957691216057308f * g * fmaf(0.044715f * g, g, 1.0f)));
     if (p.glu_limit > 0.0f) {
         g = fminf(g, p.glu_limit);
         u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
