@@ -27,6 +27,7 @@ from .base import KVNeed, Mixer, TensorSpec
 
 class LatentAttentionMixer(Mixer):
     kind = "latent_attention"
+    fuses_norm = True          # few rows: the norm before it rides on its input product, its output product adds to the stream
     fixed_shape_ok = True
 
     @classmethod
@@ -93,7 +94,10 @@ class LatentAttentionMixer(Mixer):
         self.position = (registry.position_class(spec.position.kind)(spec.position, rt)
                          if spec.position is not None else None)
 
-    def forward(self, x, step, cache) -> torch.Tensor:
+    def takes_prenormed(self, rows: int) -> bool:
+        return self.rt.few_rows_shape(rows, self.w_in) and self.w_in.shape[1] % 8 == 0
+
+    def forward(self, x, step, cache, into=None) -> torch.Tensor:
         s, rt = self.spec, self.rt
         T, H, R = x.shape[0], s.heads, s.kv_rank
         if cache is None or cache.storage is None or not cache.owner:
@@ -121,6 +125,8 @@ class LatentAttentionMixer(Mixer):
         rt.batched_product(o_lat, self.w_uv, o.transpose(0, 1))
         if s.out_gate:
             ops.sigmoid_mul(o.view(T, H * s.vdim), gate[:, :H * s.vdim])
+        if into is not None:
+            return into.product(o.view(T, H * s.vdim), self.w_o)
         return rt.linear(o.view(T, H * s.vdim), self.w_o, "mixer_out")
 
     def fast_path(self, step) -> bool:

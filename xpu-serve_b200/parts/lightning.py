@@ -25,6 +25,7 @@ from .mamba2 import chunk_plan
 
 class LightningMixer(Mixer):
     kind = "lightning"
+    fuses_norm = True          # few rows: the norm before it rides on its input product, its output product adds to the stream
     fixed_shape_ok = True      # the kernel finds every sequence's tokens in the step's description on the device
 
     @classmethod
@@ -56,7 +57,10 @@ class LightningMixer(Mixer):
         # order); unset: as many chunks as fill the device once with two CTAs an SM, between 64 and 512 tokens each.
         self.chunk = int(os.environ["XS_LIGHTNING_CHUNK"]) if "XS_LIGHTNING_CHUNK" in os.environ else None
 
-    def forward(self, x, step, cache) -> torch.Tensor:
+    def takes_prenormed(self, rows: int) -> bool:
+        return self.rt.few_rows_shape(rows, self.w_in) and self.w_in.shape[1] % 8 == 0
+
+    def forward(self, x, step, cache, into=None) -> torch.Tensor:
         s, rt = self.spec, self.rt
         if cache is None or cache.storage is None or not cache.owner:
             raise RuntimeError("lightning keeps its own state")
@@ -76,6 +80,8 @@ class LightningMixer(Mixer):
                            s.vdim, chunks)
         yn = rt.ws.get("lightning_normed", (T, vd), rt.act_dtype)
         ops.grouped_rmsnorm(y, self.w_norm, yn, 1, s.eps, gate=proj[:, 2 * qd + vd:])
+        if into is not None:
+            return into.product(yn, self.w_o)
         return rt.linear(yn, self.w_o, "mixer_out")
 
 
