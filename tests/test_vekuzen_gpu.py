@@ -158,6 +158,36 @@ def test_long_prompts_run_the_memory_in_chunks(name, dtype, replayers, folders):
     assert any(c is not None and c[0].shape[0] >= 3 for c in seen), "the long prompts did not take the chunked scan"
 
 
+def test_far_keys_through_the_model(tmp_path, dtype="float32"):
+    """One attention layer whose queries are scaled up so that each softmax rests on one or two keys, wherever they lie: the
+    oracle says that the last positions of a 200-token prompt change when only the first page's tokens change, so a lost page,
+    a key one place off or a stale latent shows. Whole, then the last 70 tokens one by one (across the borders of pages two and
+    three), then in pieces. (In float32: at 16 bits a softmax this sharp carries its own rounding past the bound; the
+    tensor-core kernels see planted keys in test_latent_attention_without_a_rotated_part.)"""
+    from xpu_serve_b200.config import VekuzenConfig
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    from xpu_serve_b200.weights import write_random_model
+    folder = str(tmp_path / "sharp")
+    write_random_model(folder, VekuzenConfig.from_json(tiny.CONFIGS["attention"]), seed=5, dtype=dtype, std=0.08,
+                       norm_range=(0.5, 1.5), scale={".mix.uq": 12.0, "pos": 2.0})
+    cfg, W = load_folder(folder)
+    toks = tiny.prompt("attention", 200, salt=2)
+    ref = plain.forward(cfg, W, toks)
+    other = plain.forward(cfg, W, [(t + 7) % 150 for t in toks[:64]] + toks[64:])
+    moved = np.abs(ref[150:] - other[150:]).max() / np.abs(ref).max()
+    tol = 2e-5
+    assert moved > 20 * tol, f"the far keys do not matter here ({moved:.2e}); scale the queries up"
+    reqs = {"far": toks, "near": tiny.prompt("attention", 66, salt=3)}
+    rp = Replayer(load_model(folder, dtype=dtype), 1024, None)
+    for steps in (tu.whole_trace(reqs), tu.tail_trace(reqs, tail=70), tu.pieces_trace(reqs, 2, pieces=(63, 2, 64, 5)), tu.batch_trace(reqs, 2)):
+        got = tu.collect(steps, tu.run_in_process(rp, steps), 150)
+        want = {("far", p): ref[p] for p in range(200) if ("far", p) in got}
+        gap, where, cos = tu.worst_gap({k: got[k] for k in want}, want)
+        assert len(want) >= 60 and gap <= tol, (len(steps), gap, where)
+    assert rp.cache.slots.held_count == 0
+
+
 def test_the_program_replays_a_trace(folders, tmp_path):
     """bin/trace_run over its standard input, in float32, against the oracle."""
     reqs = requests_for("A", [5, 40, 70])
