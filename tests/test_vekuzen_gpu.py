@@ -479,20 +479,24 @@ def test_frame_kernels_alone(dtype):
     ops.side_gate(logits[:, :d], dev_i32(ids), table.cuda(), 2 * d)
     want = plain.gelu_tanh(l0[:, :d]) * f64(table)[ids][:, 2 * d:3 * d]
     assert np.abs(f64(logits)[:, :d] - want).max() <= tol * np.abs(want).max() and np.array_equal(f64(logits)[:, d:], l0[:, d:])
-    wide = torch.from_numpy(rng.standard_normal((T, 70))).to(dtype).cuda()
-    y = torch.zeros(T, 50, dtype=dtype, device="cuda")
-    nw = torch.from_numpy(rng.uniform(0.5, 1.5, 23)).float()
-    ops.rmsnorm_rows(wide[:, 9:32], nw.cuda(), y[:, 3:26], 1e-5)
-    want = plain.unit_rms(f64(wide)[:, 9:32], 1e-5) * f64(nw)
-    assert np.abs(f64(y)[:, 3:26] - want).max() <= tol * np.abs(want).max() and float(y[:, :3].abs().max()) == 0.0 == float(y[:, 26:].abs().max())
-    o = torch.from_numpy(rng.standard_normal((T, 40))).to(dtype).cuda()
-    o0 = f64(o).copy()
-    ops.sigmoid_mul(o[:, 2:35], wide[:, 30:63])
-    assert np.abs(f64(o)[:, 2:35] - o0[:, 2:35] * plain.sigmoid(f64(wide)[:, 30:63])).max() <= tol * np.abs(o0).max()
-    assert np.array_equal(f64(o)[:, :2], o0[:, :2]) and np.array_equal(f64(o)[:, 35:], o0[:, 35:])
-    pair = torch.zeros(T, 2 * W, dtype=dtype, device="cuda")
-    ops.cast_rows(h.cuda(), pair[:, W:])
-    assert torch.equal(pair[:, W:].cpu(), h.to(dtype)) and float(pair[:, :W].abs().max()) == 0.0
+    # columns of wider matrices: at odd offsets and sizes, and in whole 16-byte pieces (the kernels of 8 elements a thread)
+    for (a, b), (ya, yb), (ga, gb), Wc in (((9, 32), (3, 26), (30, 53), 45), ((8, 40), (16, 48), (32, 64), 48)):
+        wide = torch.from_numpy(rng.standard_normal((T, 72))).to(dtype).cuda()
+        y = torch.zeros(T, 56, dtype=dtype, device="cuda")
+        nw = torch.from_numpy(rng.uniform(0.5, 1.5, b - a)).float()
+        ops.rmsnorm_rows(wide[:, a:b], nw.cuda(), y[:, ya:yb], 1e-5)
+        want = plain.unit_rms(f64(wide)[:, a:b], 1e-5) * f64(nw)
+        assert np.abs(f64(y)[:, ya:yb] - want).max() <= tol * np.abs(want).max()
+        assert float(y[:, :ya].abs().max()) == 0.0 == float(y[:, yb:].abs().max())
+        o = torch.from_numpy(rng.standard_normal((T, 56))).to(dtype).cuda()
+        o0 = f64(o).copy()
+        ops.sigmoid_mul(o[:, ya:yb], wide[:, ga:gb])
+        assert np.abs(f64(o)[:, ya:yb] - o0[:, ya:yb] * plain.sigmoid(f64(wide)[:, ga:gb])).max() <= tol * np.abs(o0).max()
+        assert np.array_equal(f64(o)[:, :ya], o0[:, :ya]) and np.array_equal(f64(o)[:, yb:], o0[:, yb:])
+        hw = torch.from_numpy(rng.standard_normal((T, Wc))).float()
+        pair = torch.zeros(T, 2 * Wc, dtype=dtype, device="cuda")
+        ops.cast_rows(hw.cuda(), pair[:, Wc:])
+        assert torch.equal(pair[:, Wc:].cpu(), hw.to(dtype)) and float(pair[:, :Wc].abs().max()) == 0.0
     for F, inter in ((13, 0), (16, 8), (24, 0)):
         gu = torch.from_numpy(rng.standard_normal((T, 2 * F)) * 2).to(dtype).cuda()
         act = torch.empty(T, F, dtype=dtype, device="cuda")

@@ -331,6 +331,88 @@ __global__ void rmsnorm_accumulate_kernel(const T* __restrict__ x, const float* 
     }
 }
 
+
+// The same three for bfloat16 rows in whole 16-byte pieces (n and the row strides multiples of 8, aligned pointers): 8 elements a
+// thread and load.
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&v)[8]) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h2[j]);
+        v[2 * j] = f.x;
+        v[2 * j + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
+    uint4 o;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    return o;
+}
+
+// One block a row, the row held in registers (up to 4 pieces a thread: n <= 32 * blockDim.x).
+__global__ void rmsnorm_rows_vec_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ w,
+                                        __nv_bfloat16* __restrict__ y, int64_t ldy, int n, float eps) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const __nv_bfloat16* xr = x + (int64_t)blockIdx.x * ldx;
+    __nv_bfloat16* yr = y + (int64_t)blockIdx.x * ldy;
+    float v[4][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int c = (threadIdx.x + u * blockDim.x) * 8;
+        if (c < n) {
+            unpack_bf16x8(*reinterpret_cast<const uint4*>(xr + c), v[u]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss = fmaf(v[u][j], v[u][j], ss);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int c = (threadIdx.x + u * blockDim.x) * 8;
+        if (c < n) {
+            const float4 w0 = *reinterpret_cast<const float4*>(w + c), w1 = *reinterpret_cast<const float4*>(w + c + 4);
+            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[u][j] = v[u][j] * inv * ww[j];
+            *reinterpret_cast<uint4*>(yr + c) = pack_bf16x8(v[u]);
+        }
+    }
+}
+
+__global__ void sigmoid_mul_vec_kernel(__nv_bfloat16* __restrict__ o, int64_t ldo, const __nv_bfloat16* __restrict__ g, int64_t ldg,
+                                       int64_t total8, int n8) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / n8;
+        const int c = (int)(i - t * n8) * 8;
+        float a[8], b[8];
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(o + t * ldo + c), a);
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(g + t * ldg + c), b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = a[j] / (1.0f + expf(-b[j]));
+        *reinterpret_cast<uint4*>(o + t * ldo + c) = pack_bf16x8(a);
+    }
+}
+
+__global__ void cast_rows_vec_kernel(const float* __restrict__ src, int64_t lds, __nv_bfloat16* __restrict__ dst, int64_t ldd,
+                                     int64_t total8, int n8) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / n8;
+        const int c = (int)(i - t * n8) * 8;
+        const float4 a = *reinterpret_cast<const float4*>(src + t * lds + c), b = *reinterpret_cast<const float4*>(src + t * lds + c + 4);
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        *reinterpret_cast<uint4*>(dst + t * ldd + c) = pack_bf16x8(v);
+    }
+}
+
 }  // namespace
 
 XS_API int xs_embed_pos(const void* table, const void* rows, int dtype, const int32_t* ids, const int32_t* positions, float* h,
@@ -361,6 +443,13 @@ XS_API int xs_rmsnorm_rows(const void* x, int64_t ldx, const float* w, void* y, 
                            cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && n > 0 && ldx >= n && ldy >= n, "rmsnorm_rows: %d rows of %d", T, n);
+    if (dtype == XS_BF16 && n % 8 == 0 && n <= 8192 && ldx % 8 == 0 && ldy % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 &&
+        (uintptr_t)w % 16 == 0) {
+        xs_launch(rmsnorm_rows_vec_kernel, dim3(T), dim3(n > 4096 ? 256 : 128), 0, stream, (const __nv_bfloat16*)x, ldx, w,
+                  (__nv_bfloat16*)y, ldy, n, eps);
+        XS_LAUNCH_CHECK("rmsnorm_rows");
+        return 0;
+    }
     XS_DISPATCH_DTYPE(dtype, TT, xs_launch(rmsnorm_rows_kernel<TT>, dim3(T), dim3(n >= 1024 ? 256 : 128), 0, stream, (const TT*)x, ldx,
                                            w, (TT*)y, ldy, n, eps));
     XS_LAUNCH_CHECK("rmsnorm_rows");
@@ -370,6 +459,14 @@ XS_API int xs_rmsnorm_rows(const void* x, int64_t ldx, const float* w, void* y, 
 XS_API int xs_sigmoid_mul(void* o, int64_t ldo, const void* g, int64_t ldg, int T, int n, int dtype, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && n > 0 && ldo >= n && ldg >= n, "sigmoid_mul: %d rows of %d", T, n);
+    if (dtype == XS_BF16 && n % 8 == 0 && ldo % 8 == 0 && ldg % 8 == 0 && (uintptr_t)o % 16 == 0 && (uintptr_t)g % 16 == 0) {
+        const int64_t total8 = (int64_t)T * (n / 8);
+        const int blocks8 = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        xs_launch(sigmoid_mul_vec_kernel, dim3(blocks8), dim3(256), 0, stream, (__nv_bfloat16*)o, ldo, (const __nv_bfloat16*)g, ldg,
+                  total8, n / 8);
+        XS_LAUNCH_CHECK("sigmoid_mul");
+        return 0;
+    }
     const int64_t total = (int64_t)T * n;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     XS_DISPATCH_DTYPE(dtype, TT, xs_launch(sigmoid_mul_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (TT*)o, ldo, (const TT*)g, ldg,
@@ -381,6 +478,13 @@ XS_API int xs_sigmoid_mul(void* o, int64_t ldo, const void* g, int64_t ldg, int 
 XS_API int xs_cast_rows(const float* src, int64_t lds, void* dst, int64_t ldd, int T, int n, int dtype, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && n > 0 && lds >= n && ldd >= n, "cast_rows: %d rows of %d", T, n);
+    if (dtype == XS_BF16 && n % 8 == 0 && lds % 4 == 0 && ldd % 8 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)dst % 16 == 0) {
+        const int64_t total8 = (int64_t)T * (n / 8);
+        const int blocks8 = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        xs_launch(cast_rows_vec_kernel, dim3(blocks8), dim3(256), 0, stream, src, lds, (__nv_bfloat16*)dst, ldd, total8, n / 8);
+        XS_LAUNCH_CHECK("cast_rows");
+        return 0;
+    }
     const int64_t total = (int64_t)T * n;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     XS_DISPATCH_DTYPE(dtype, TT, xs_launch(cast_rows_kernel<TT>, dim3(blocks), dim3(256), 0, stream, src, lds, (TT*)dst, ldd, total, n));
