@@ -175,3 +175,13 @@ def test_plain_running_order_and_first_tokens():
     streams = []
     plain.forward(cfg, W, toks, streams)
     assert len(streams) == 6
+
+
+def test_the_bench_stacks_are_valid_configurations():
+    """`bench.py --workload vekuzen`: every stack and the stack beside it parse, at equal width and vocabulary."""
+    import bench
+    for name in bench.VEKUZEN_STACKS:
+        ours, (label, beside) = bench.vekuzen_stack_configs(name)
+        a, b = ours.model_spec(), beside.model_spec()
+        assert isinstance(ours, VekuzenConfig) and label in ("saralix", "nimelorn")
+        assert (a.hidden, a.vocab, len(a.layers)) == (b.hidden, b.vocab, len(b.layers)) == (2048, 32768, 2)
